@@ -34,10 +34,12 @@ class KVGroup:
         self.pages = GroupPages(n_pages, page_size, need.window)
         shape = (len(places), n_pages, need.n_kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        # a latent that is key and value at once is kept once
+        self.v = self.k if need.values_are_keys else torch.zeros(shape, dtype=dtype, device=device)
 
     def bytes_per_position(self) -> int:
-        return 2 * len(self.places) * self.need.n_kv_heads * self.need.head_dim * self.k.element_size()
+        kinds = 1 if self.need.values_are_keys else 2
+        return kinds * len(self.places) * self.need.n_kv_heads * self.need.head_dim * self.k.element_size()
 
 
 class CacheStorage:

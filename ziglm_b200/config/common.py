@@ -80,10 +80,13 @@ def token_ids(d: Mapping[str, Any], key: str) -> Tuple[int, ...]:
 
 
 def architecture_name(d: Any) -> str:
-    """``architectures[0]`` of a config.json dictionary: the key of the registry."""
+    """``architectures[0]`` of a config.json dictionary, or its ``architecture`` when the file names one
+    design as a plain string: the key of the registry."""
     arch = d.get("architectures") if isinstance(d, Mapping) else None
+    if arch is None and isinstance(d, Mapping) and isinstance(d.get("architecture"), str) and d["architecture"]:
+        return d["architecture"]
     if not (isinstance(arch, (list, tuple)) and arch and isinstance(arch[0], str)):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' a name)")
     return arch[0]
 
 

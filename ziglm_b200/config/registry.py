@@ -14,6 +14,7 @@ from typing import Any, Callable, Dict, Mapping
 
 from .common import ConfigError, architecture_name, read_config_json
 from .llama import LlamaConfig
+from .tumatar import TumatarConfig
 from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -62,3 +63,4 @@ def config_from_folder(folder: str):
 
 
 register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
+register_architecture(TumatarConfig.ARCHITECTURE, TumatarConfig)

@@ -79,8 +79,8 @@ class LayerSpec:
     prefix: str                    # tensor-name prefix of this layer's weights
     mixer_norm: NormSpec
     mixer: MixerSpec
-    ffn_norm: NormSpec
-    ffn: FeedForwardSpec
+    ffn_norm: Optional[NormSpec]   # None together with ``ffn``: the layer has no feed-forward
+    ffn: Optional[FeedForwardSpec]
     # local parameter name (as the part declares it) -> name under ``prefix``
     names: Mapping[str, str] = field(default_factory=dict)
     options: Mapping[str, Any] = field(default_factory=dict)
@@ -112,6 +112,9 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     embed_hook: Optional[HookSpec] = None      # runs on the float32 residual [T, width] after the embedding
     logits_hook: Optional[HookSpec] = None     # runs on the float32 logits [n_want, vocab] after the head
+    # place of the schedule -> a hook that runs on the float32 residual right before that place's block (a vector
+    # added at the start of every pass through a repeated run of layers, say)
+    place_hooks: Mapping[int, HookSpec] = field(default_factory=dict)
     options: Mapping[str, Any] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
@@ -122,3 +125,8 @@ class ModelSpec:
             src = layer.mixer.cache_from
             if src is not None and not 0 <= src < len(self.layers):
                 raise ValueError(f"layer {i} reads the cache of layer {src}, which does not exist")
+            if (layer.ffn is None) != (layer.ffn_norm is None):
+                raise ValueError(f"layer {i}: a feed-forward and its norm come together or not at all")
+        for place in self.place_hooks:
+            if not 0 <= place < len(self.schedule):
+                raise ValueError(f"a hook is hung before place {place}, but the schedule has {len(self.schedule)} places")

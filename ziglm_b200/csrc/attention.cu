@@ -68,7 +68,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_he
     }
     const long kv_head_stride = (long)page_size * hd;
     // this block's share of the heads, counted over q heads, k heads, v heads in that order
-    const int total_heads = n_heads + 2 * n_kv;
+    const int total_heads = n_heads + n_kv + (v_pages != nullptr ? n_kv : 0);   // no value pages: the rows hold no value heads
     const int per = (total_heads + gridDim.y - 1) / gridDim.y;
     const int h_lo = blockIdx.y * per, h_hi = min(total_heads, h_lo + per);
     const int rot_hi = min(h_hi, n_heads + n_kv);            // heads below this one are rotated
@@ -136,7 +136,7 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_
     pdl_wait();
     __nv_bfloat16* row0 = qkv + (long)t * row_stride;
     const long kv_head_stride = (long)page_size * hd;
-    const int total_heads = n_heads + 2 * n_kv;
+    const int total_heads = n_heads + n_kv + (v_pages != nullptr ? n_kv : 0);   // no value pages: the rows hold no value heads
     const int per = (total_heads + gridDim.y - 1) / gridDim.y;
     const int h_lo = blockIdx.y * per, h_hi = min(total_heads, h_lo + per);
     const int rot_hi = min(h_hi, n_heads + n_kv);
@@ -199,7 +199,7 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_
 //   split   grid (T, n_heads / G, parts): a block computes one part and stores it in scratch memory, and
 //           attention_fold_kernel folds a token's parts (steps of few tokens: the parts give the blocks).
 constexpr int ATT_WARPS = 4;
-constexpr int ATT_MAX_HD = 256;
+constexpr int ATT_MAX_HD = 512;
 constexpr int ATT_PART = ATT_WARPS * 2 * 32;
 
 // k[d..d+VEC) of one key row as floats
@@ -257,10 +257,15 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
         q_s[i / hd][i % hd] = to_float(q[(long)t * q_row_stride + (long)(h0 + i / hd) * hd + i % hd]);
     __syncthreads();
 
-    // the running result: thread x owns dimensions x and x + 128 of every head
-    float run_m[G], run_l[G], run_o[G][2];
+    // the running result: thread x owns dimensions x, x + 128, ... of every head
+    constexpr int NRUN = NREG / 4;
+    float run_m[G], run_l[G], run_o[G][NRUN];
 #pragma unroll
-    for (int g = 0; g < G; ++g) { run_m[g] = -INFINITY; run_l[g] = 0.f; run_o[g][0] = run_o[g][1] = 0.f; }
+    for (int g = 0; g < G; ++g) {
+        run_m[g] = -INFINITY; run_l[g] = 0.f;
+#pragma unroll
+        for (int r = 0; r < NRUN; ++r) run_o[g][r] = 0.f;
+    }
 
     for (int part = p_lo; part < p_hi; ++part) {
         float acc[G][NREG], m[G], l[G];
@@ -351,7 +356,7 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
             float a, bb, m_new;
             fold_weights(run_m[g], big, m_new, a, bb);
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
+            for (int r = 0; r < NRUN; ++r) {
                 const int d = threadIdx.x + r * ATT_WARPS * 32;
                 if (d < hd) {
                     float op = 0.f;
@@ -376,7 +381,7 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
+        for (int r = 0; r < NRUN; ++r) {
             const int d = threadIdx.x + r * ATT_WARPS * 32;
             if (d < hd) out[((long)t * n_heads + h0 + g) * hd + d] = from_float<T>(run_o[g][r] / run_l[g]);
         }
@@ -393,12 +398,13 @@ attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, cons
     const int n_parts = (pos - start + 1 + ATT_PART - 1) / ATT_PART;
     const float* ml = part_ml + ((long)t * n_heads + h) * max_parts * 2;
     const float* po = part_o + ((long)t * n_heads + h) * max_parts * hd;
-    float run_m = -INFINITY, run_l = 0.f, run_o[2] = {0.f, 0.f};
+    constexpr int NRUN = ATT_MAX_HD / (ATT_WARPS * 32);
+    float run_m = -INFINITY, run_l = 0.f, run_o[NRUN] = {};
     for (int part = 0; part < n_parts; ++part) {
         float a, bb, m_new;
         fold_weights(run_m, ml[2 * part], m_new, a, bb);
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
+        for (int r = 0; r < NRUN; ++r) {
             const int d = threadIdx.x + r * ATT_WARPS * 32;
             if (d < hd) run_o[r] = fold_value(run_o[r], a, po[(long)part * hd + d], bb);
         }
@@ -406,7 +412,7 @@ attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, cons
         run_m = m_new;
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NRUN; ++r) {
         const int d = threadIdx.x + r * ATT_WARPS * 32;
         if (d < hd) out[((long)t * n_heads + h) * hd + d] = from_float<T>(run_o[r] / run_l);
     }
@@ -418,14 +424,14 @@ static int launch_attention(const void* q, long q_row_stride, void* out, int T_,
                             int bt_stride, const void* k_pages, const void* v_pages, int page_size, long page_stride,
                             float* part_ml, float* part_o, int max_parts, cudaStream_t stream) {
     dim3 grid(T_, n_heads / G, part_o ? max_parts : 1);
-    if (hd <= 128)
-        attention_general_kernel<T, VEC, G, 4><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token, block_table,
-            bt_stride, (const T*)k_pages, (const T*)v_pages, page_size, page_stride, part_ml, part_o, max_parts);
-    else
-        attention_general_kernel<T, VEC, G, 8><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token, block_table,
-            bt_stride, (const T*)k_pages, (const T*)v_pages, page_size, page_stride, part_ml, part_o, max_parts);
+#define ZLM_ATT_GO(NREG)                                                                                              \
+    attention_general_kernel<T, VEC, G, NREG><<<grid, ATT_WARPS * 32, 0, stream>>>(                                     \
+        (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token, block_table,     \
+        bt_stride, (const T*)k_pages, (const T*)v_pages, page_size, page_stride, part_ml, part_o, max_parts)
+    if (hd <= 128) ZLM_ATT_GO(4);
+    else if (hd <= 256) ZLM_ATT_GO(8);
+    else ZLM_ATT_GO(16);
+#undef ZLM_ATT_GO
     int rc = launch_status();
     if (rc || !part_o) return rc;
     attention_fold_kernel<T><<<dim3(T_, n_heads), ATT_WARPS * 32, 0, stream>>>((T*)out, n_heads, hd, window, positions,
@@ -442,7 +448,7 @@ static int pick_group(int group, const void* q, long q_row_stride, void* out, in
     launch_attention<T, VEC, GV>(q, q_row_stride, out, T_, n_heads, n_kv, hd, scale, window, positions, seq_of_token,   \
                                  block_table, bt_stride, k_pages, v_pages, page_size, page_stride, part_ml, part_o,     \
                                  max_parts, stream)
-    if (group % 4 == 0) return ZLM_ATT(4);
+    if (group % 4 == 0 && hd <= 256) return ZLM_ATT(4);
     if (group % 2 == 0) return ZLM_ATT(2);
     return ZLM_ATT(1);
 #undef ZLM_ATT
@@ -454,7 +460,8 @@ using namespace zlm;
 
 // Rotates q and k in place inside qkv and copies k (rotated) and v into the cache.
 // inv_freq == nullptr: no rotation.  k_pages == nullptr: nothing is stored (a layer
-// that reads another layer's cache).
+// that reads another layer's cache).  v_pages == nullptr with k_pages: the rows are [q | k] and only the keys
+// are stored (a latent that serves as key and value).
 ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int n_heads, int n_kv, int hd, int rot,
                               const float* inv_freq, const int* positions, const int* seq_of_token,
                               const int* block_table, int bt_stride, void* k_pages, void* v_pages, int page_size,
@@ -464,7 +471,7 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
         return ZLM_ERR_BAD_ARG;
     if (rot / 2 > ROPE_MAX_HALF) return ZLM_ERR_UNSUPPORTED;
     // few tokens (a decode step): the heads of a token are shared out over several blocks
-    const int total_heads = n_heads + 2 * n_kv;
+    const int total_heads = n_heads + n_kv + (v_pages != nullptr ? n_kv : 0);
     int parts = (296 + T - 1) / T;
     if (parts > total_heads) parts = total_heads;
     if (parts < 1) parts = 1;
@@ -479,7 +486,7 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
                        hd, rot, inv_freq, positions, seq_of_token, block_table, bt_stride, (float*)k_pages,
                        (float*)v_pages, page_size, page_stride);
     else if (dtype == ZLM_BF16 && hd % 8 == 0 && rot % 16 == 0 && row_stride % 8 == 0 && page_stride % 8 == 0 &&
-             (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0)
+             (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0 && hd / 2 <= 2048)
         e = launch_pdl(rope_store_vec_kernel, grid, dim3(work >= 256 * 8 ? 256 : (work >= 128 * 8 ? 128 : 64)), 0, stream,
                        (__nv_bfloat16*)qkv, row_stride, n_heads, n_kv, hd, rot, inv_freq, positions, seq_of_token,
                        block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, page_stride);
@@ -496,7 +503,7 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
 // is max_keys keys over more blocks (0: the step has enough tokens, or one part of keys).
 ZLM_EXPORT long zlm_attention_general_scratch(int T, int n_heads, int n_kv, int hd, int max_keys) {
     if (T <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return 0;
-    const int group = n_heads / n_kv, g = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+    const int group = n_heads / n_kv, g = (group % 4 == 0 && hd <= 256) ? 4 : (group % 2 == 0 ? 2 : 1);
     const long parts = (max_keys + ATT_PART - 1) / ATT_PART;
     if (parts <= 1 || (long)T * (n_heads / g) >= 2 * 148) return 0;
     return (long)T * n_heads * parts * (hd + 2);

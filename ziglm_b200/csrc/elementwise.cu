@@ -117,7 +117,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 // interleaved != 0: gate j in column 2j, up j in column 2j+1.
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int I, int kind,
-                                 int interleaved) {
+                                 int interleaved, float limit, float slope) {
     pdl_launch_dependents();
     pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -127,6 +127,13 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     const float g = to_float(gu[t * 2 * I + (interleaved ? 2 * j : j)]);
     const float u = to_float(gu[t * 2 * I + (interleaved ? 2 * j + 1 : I + j)]);
     float a;
+    if (kind == 2) {
+        // clamped swish: g' = min(g, L), u' = clamp(u, -L, L); g' sigmoid(slope g') (u' + 1)
+        const float gc = fminf(g, limit);
+        const float uc = fminf(fmaxf(u, -limit), limit);
+        out[idx] = from_float<T>((gc / (1.0f + expf(-slope * gc))) * (uc + 1.0f));
+        return;
+    }
     if (kind == 0) {
         a = g / (1.0f + expf(-g));                         // silu
     } else {
@@ -134,6 +141,47 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
         a = 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
     }
     out[idx] = from_float<T>(a * u);
+}
+
+// A norm over a row that is a slice of a wider row (x and out with row strides of their own), and the same
+// norm added into a float32 row (the norm behind a sublayer, summed into the residual stream in one pass):
+//   out[r, i] (+)= x[r, i] / sqrt(mean_i x[r, i]^2 + eps) * (w[i] + weight_offset)
+template <typename TW, typename TO, bool ADD>
+__global__ void rmsnorm_strided_kernel(const float* __restrict__ x, long x_stride, const TW* __restrict__ w,
+                                       TO* __restrict__ out, long out_stride, int d, float eps, float weight_offset) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* xr = x + (long)blockIdx.x * x_stride;
+    TO* o = out + (long)blockIdx.x * out_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float y = (xr[i] * inv) * (to_float(w[i]) + weight_offset);
+        if (ADD) o[i] = from_float<TO>(to_float(o[i]) + y);
+        else o[i] = from_float<TO>(y);
+    }
+}
+
+// x[t, :] += table[row, :] for every row t of x (a learned vector added to the whole step)
+template <typename TW>
+__global__ void add_row_kernel(float* __restrict__ x, const TW* __restrict__ table_row, long total, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] += to_float(table_row[i % d]);
+}
+
+__global__ void scale_kernel(float* __restrict__ x, long n, float factor) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= factor;
 }
 
 // y += x (float), used by parts that cannot fold their residual sum into a product
@@ -276,22 +324,65 @@ ZLM_EXPORT int zlm_rmsnorm(const float* x, const void* w, int w_dtype, void* out
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
+// kind 0 silu, 1 gelu (tanh form), 2 clamped swish with (limit, slope); the two floats are read by kind 2 only
 ZLM_EXPORT int zlm_gated_act(const void* gu, void* out, int dtype, int T, int I, int kind, int interleaved,
-                             cudaStream_t stream) {
+                             float limit, float slope, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (I <= 0 || (kind != 0 && kind != 1)) return ZLM_ERR_BAD_ARG;
+    if (I <= 0 || kind < 0 || kind > 2) return ZLM_ERR_BAD_ARG;
     const long total = (long)T * I;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     cudaError_t e;
     if (dtype == ZLM_F32)
         e = launch_pdl(gated_act_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out,
-                       total, I, kind, interleaved);
+                       total, I, kind, interleaved, limit, slope);
     else if (dtype == ZLM_BF16)
         e = launch_pdl(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
-                       (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, I, kind, interleaved);
+                       (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, I, kind, interleaved, limit, slope);
     else
         return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// out rows (stride out_stride, storage out_dtype) = or += the RMS norm of x rows (float, stride x_stride).
+ZLM_EXPORT int zlm_rmsnorm_strided(const float* x, long x_stride, const void* w, int w_dtype, void* out, int out_dtype,
+                                   long out_stride, int add, int n_rows, int d, float eps, float weight_offset,
+                                   cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0 || (add && out_dtype != ZLM_F32)) return ZLM_ERR_BAD_ARG;
+    const int threads = norm_threads(d);
+    cudaError_t e;
+#define ZLM_NORM_S(TW, TO, ADD)                                                                                      \
+    e = launch_pdl(rmsnorm_strided_kernel<TW, TO, ADD>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, (const TW*)w, \
+                   (TO*)out, out_stride, d, eps, weight_offset)
+    if (w_dtype == ZLM_F32 && out_dtype == ZLM_F32) { if (add) ZLM_NORM_S(float, float, true); else ZLM_NORM_S(float, float, false); }
+    else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_F32) { if (add) ZLM_NORM_S(__nv_bfloat16, float, true); else ZLM_NORM_S(__nv_bfloat16, float, false); }
+    else if (w_dtype == ZLM_F32 && out_dtype == ZLM_BF16) ZLM_NORM_S(float, __nv_bfloat16, false);
+    else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_BF16) ZLM_NORM_S(__nv_bfloat16, __nv_bfloat16, false);
+    else return ZLM_ERR_UNSUPPORTED;
+#undef ZLM_NORM_S
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+ZLM_EXPORT int zlm_add_row(float* x, const void* table_row, int dtype, int T, int d, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0) return ZLM_ERR_BAD_ARG;
+    const long total = (long)T * d;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(add_row_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)table_row, total, d);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(add_row_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x,
+                       (const __nv_bfloat16*)table_row, total, d);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+ZLM_EXPORT int zlm_scale(float* x, long n, float factor, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    cudaError_t e = launch_pdl(scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, factor);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 

@@ -1,0 +1,165 @@
+// A gated linear recurrence behind a short causal convolution, per channel:
+//   u_t   = cb + sum_j taps[K-1-j] * x_{t-j}                 (j = 0 is the current token; zeros before the start)
+//   a_t   = exp(-rate * r_t * softplus(lam)),   r_t, i_t: gates in (0, 1) computed from u_t by the caller
+//   S_t   = a_t * S_{t-1} + sqrt(1 - a_t^2) * i_t * u_t      (S = 0 before the first token, no special case)
+//   out_t = S_t * gelu_tanh(y_t)
+// What a sequence carries from step to step is [K, C] floats per sequence: rows 0..K-2 hold the last K-1
+// inputs x (oldest first), row K-1 holds S.  Decays, gates, the state and every product that enters the
+// recurrence are float in both precisions; sqrt(1 - a^2) is taken as sqrt(-expm1(2 log a)), which stays exact
+// when a is close to 1.
+//
+// The recurrence is a composition of affine maps S -> a S + b, which is associative: a block takes one
+// sequence and 32 channels, cuts the sequence's tokens of this step into as many chunks as it has rows of
+// threads, every thread composes the maps of its chunk, the chunks' maps are folded in order to give each
+// chunk its incoming state, and a second pass over the chunk writes the outputs.
+#include "common.cuh"
+
+namespace zlm {
+
+constexpr int RC_CH = 32;        // channels a block takes
+constexpr int RC_MAX_CHUNKS = 32;
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// u[t, c] for every token of the step; reads the inputs before the step from the sequence's state.
+template <typename T>
+__global__ void conv_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ taps,
+                            const float* __restrict__ bias, const float* __restrict__ state, long state_stride,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens,
+                            const int* __restrict__ slots, T* __restrict__ u, int n_tokens, int C, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)n_tokens * C) return;
+    const int t = (int)(idx / C), c = (int)(idx % C);
+    const int b = seq_of_token[t];
+    const int i = t - cu_seqlens[b];                  // index of the token among its sequence's tokens of this step
+    const float* st = state + (long)slots[b] * state_stride;
+    float acc = bias[c];
+    for (int j = K - 1; j >= 0; --j) {                // oldest input first
+        const float xv = (i - j >= 0) ? to_float(x[(long)(t - j) * x_stride + c])
+                                      : st[(long)(K - 1 + i - j) * C + c];
+        acc = fmaf(taps[(long)c * K + (K - 1 - j)], xv, acc);
+    }
+    u[idx] = from_float<T>(acc);
+}
+
+// grid (sequences, ceil(C / 32)), block (32, chunks)
+template <typename T>
+__global__ void __launch_bounds__(RC_CH * RC_MAX_CHUNKS)
+scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, int gate_block, const T* __restrict__ y,
+            long y_stride, const T* __restrict__ x, long x_stride, const float* __restrict__ lam, float rate,
+            float* __restrict__ state, long state_stride, const int* __restrict__ cu_seqlens,
+            const int* __restrict__ slots, T* __restrict__ out, int C, int K) {
+    __shared__ float agg_a[RC_MAX_CHUNKS][RC_CH], agg_b[RC_MAX_CHUNKS][RC_CH];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int c = blockIdx.y * RC_CH + threadIdx.x;
+    const int chunk = threadIdx.y, n_chunks = blockDim.y;
+    const int first = cu_seqlens[b], n_new = cu_seqlens[b + 1] - first;
+    const int per = (n_new + n_chunks - 1) / n_chunks;
+    const int lo = first + min(n_new, chunk * per), hi = first + min(n_new, (chunk + 1) * per);
+    const bool live = c < C;
+    float* st = state + (long)slots[b] * state_stride;
+    float sp = 0.f;
+    long g_r = 0;
+    if (live) {
+        sp = rate * softplus_f(lam[c]);
+        g_r = (long)(c / gate_block) * 2 * gate_block + c % gate_block;     // its input gate lies gate_block further
+    }
+    const long g_stride = 2L * C;
+    // pass 1: the chunk's map S -> A S + B
+    float A = 1.f, B = 0.f;
+    if (live) {
+        for (int t = lo; t < hi; ++t) {
+            const float r = gates[(long)t * g_stride + g_r], ig = gates[(long)t * g_stride + g_r + gate_block];
+            const float uv = to_float(u[(long)t * C + c]);
+            const float log_a = -sp * r;
+            const float a = expf(log_a);
+            const float bb = sqrtf(-expm1f(2.f * log_a)) * (ig * uv);
+            A *= a;
+            B = fmaf(a, B, bb);
+        }
+    }
+    agg_a[chunk][threadIdx.x] = A;
+    agg_b[chunk][threadIdx.x] = B;
+    __syncthreads();
+    if (!live) return;
+    // the state that enters this chunk: the earlier chunks' maps applied in order to the carried state
+    float S = st[(long)(K - 1) * C + c];
+    for (int j = 0; j < chunk; ++j) S = fmaf(agg_a[j][threadIdx.x], S, agg_b[j][threadIdx.x]);
+    // pass 2: the outputs
+    for (int t = lo; t < hi; ++t) {
+        const float r = gates[(long)t * g_stride + g_r], ig = gates[(long)t * g_stride + g_r + gate_block];
+        const float uv = to_float(u[(long)t * C + c]);
+        const float log_a = -sp * r;
+        const float a = expf(log_a);
+        S = fmaf(a, S, sqrtf(-expm1f(2.f * log_a)) * (ig * uv));
+        out[(long)t * C + c] = from_float<T>(S * gelu_tanh_f(to_float(y[(long)t * y_stride + c])));
+    }
+    if (chunk != n_chunks - 1) return;
+    // the last chunk leaves the state: S after the last token, and the last K-1 inputs (rows in ascending order:
+    // row j takes what row j + n_new held, which is overwritten only later)
+    st[(long)(K - 1) * C + c] = S;
+    for (int j = 0; j < K - 1; ++j) {
+        const int i = n_new - (K - 1) + j;           // index among the step's tokens, negative: an older input
+        st[(long)j * C + c] = i >= 0 ? to_float(x[(long)(first + i) * x_stride + c]) : st[(long)(j + n_new) * C + c];
+    }
+}
+
+}  // namespace zlm
+
+using namespace zlm;
+
+// x: [T, C] rows with stride x_stride (the convolution's inputs); taps: float [C, K]; bias: float [C];
+// state: float [slots, K, C]; u: [T, C] contiguous.
+ZLM_EXPORT int zlm_causal_conv(const void* x, int dtype, long x_stride, const float* taps, const float* bias,
+                               const float* state, long state_stride, const int* seq_of_token, const int* cu_seqlens,
+                               const int* slots, void* u, int n_tokens, int C, int K, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (C <= 0 || K <= 0) return ZLM_ERR_BAD_ARG;
+    const long total = (long)n_tokens * C;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(conv_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, x_stride, taps, bias, state,
+                       state_stride, seq_of_token, cu_seqlens, slots, (float*)u, n_tokens, C, K);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, x_stride,
+                       taps, bias, state, state_stride, seq_of_token, cu_seqlens, slots, (__nv_bfloat16*)u, n_tokens, C, K);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// u: [T, C]; gates: float [T, 2C], for each block of gate_block channels first its recurrence gates then its
+// input gates; y, x: [T, C] rows with strides; lam: float [C]; out: [T, C]; max_new: the most tokens a sequence
+// brings (sizes the chunks).
+ZLM_EXPORT int zlm_gated_scan(const void* u, int dtype, const float* gates, int gate_block, const void* y, long y_stride,
+                              const void* x, long x_stride, const float* lam, float rate, float* state,
+                              long state_stride, const int* cu_seqlens, const int* slots, void* out, int n_seqs,
+                              int max_new, int C, int K, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (C <= 0 || K <= 0 || gate_block <= 0 || C % gate_block || max_new <= 0) return ZLM_ERR_BAD_ARG;
+    if ((C + RC_CH - 1) / RC_CH > 65535) return ZLM_ERR_UNSUPPORTED;
+    int chunks = (max_new + 15) / 16;                 // a chunk of fewer than 16 tokens is not worth a thread
+    if (chunks > RC_MAX_CHUNKS) chunks = RC_MAX_CHUNKS;
+    dim3 grid(n_seqs, (C + RC_CH - 1) / RC_CH), block(RC_CH, chunks);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(scan_kernel<float>, grid, block, 0, stream, (const float*)u, gates, gate_block, (const float*)y,
+                       y_stride, (const float*)x, x_stride, lam, rate, state, state_stride, cu_seqlens, slots,
+                       (float*)out, C, K);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(scan_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)u, gates, gate_block,
+                       (const __nv_bfloat16*)y, y_stride, (const __nv_bfloat16*)x, x_stride, lam, rate, state,
+                       state_stride, cu_seqlens, slots, (__nv_bfloat16*)out, C, K);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}

@@ -31,10 +31,13 @@ def declare_parameters(spec: ModelSpec) -> Dict[str, ParamDecl]:
         out[_final_norm_name(spec, local)] = decl
     if spec.head_name is not None:
         out[spec.head_name] = ParamDecl((spec.vocab_size, spec.width))
-    for hook in (spec.embed_hook, spec.logits_hook):
+    for hook in (spec.embed_hook, spec.logits_hook) + tuple(spec.place_hooks.values()):
         if hook is not None:
             for local, decl in hook_class(hook.kind).declare(hook).items():
-                out[hook.names.get(local, local)] = decl
+                name = hook.names.get(local, local)
+                if name in out and out[name] != decl:
+                    raise ValueError(f"tensor {name!r} is declared twice with different shapes")
+                out[name] = decl
     return out
 
 
@@ -54,6 +57,7 @@ class Model:
         self.final_norm = norm_class(spec.final_norm.kind)(spec.final_norm, dtype, device)
         self.embed_hook = hook_class(spec.embed_hook.kind)(spec.embed_hook, dtype, device) if spec.embed_hook else None
         self.logits_hook = hook_class(spec.logits_hook.kind)(spec.logits_hook, dtype, device) if spec.logits_hook else None
+        self.place_hooks = {place: hook_class(h.kind)(h, dtype, device) for place, h in spec.place_hooks.items()}
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
 
@@ -71,7 +75,9 @@ class Model:
                               for name in norm_class(spec.final_norm.kind).declare(spec.final_norm)})
         head_weight = self.embedding if spec.head_name is None else tensors[spec.head_name]
         self.head = Linear(head_weight)
-        for hook_spec, hook in ((spec.embed_hook, self.embed_hook), (spec.logits_hook, self.logits_hook)):
+        hooks = [(spec.embed_hook, self.embed_hook), (spec.logits_hook, self.logits_hook)]
+        hooks += [(spec.place_hooks[place], hook) for place, hook in self.place_hooks.items()]
+        for hook_spec, hook in hooks:
             if hook is not None:
                 hook.bind({local: tensors[hook_spec.names.get(local, local)]
                            for local in hook_class(hook_spec.kind).declare(hook_spec)})
@@ -82,7 +88,7 @@ class Model:
             libs += b.kernel_libraries()
         if self.head is not None:
             libs += self.head.libraries(self.dtype)
-        for hook in (self.embed_hook, self.logits_hook):
+        for hook in (self.embed_hook, self.logits_hook) + tuple(self.place_hooks.values()):
             if hook is not None:
                 libs += hook.kernel_libraries()
         return tuple(dict.fromkeys(libs))
@@ -120,9 +126,12 @@ class Model:
         carried = None           # the next block's first norm, half done by the block before (steps of few tokens)
         for place, li in enumerate(spec.schedule):
             block = self.blocks[li]
+            if place in self.place_hooks:
+                self.place_hooks[place].forward(step, x)
             nxt = self.blocks[spec.schedule[place + 1]] if place + 1 < len(spec.schedule) else None
             takes = getattr(nxt, "accepts_normed_input", None)
-            next_norm = nxt.mixer_norm if takes is not None and takes() else None
+            # a hook before the next block changes x after this block is done: its norm cannot ride on this one
+            next_norm = nxt.mixer_norm if takes is not None and takes() and place + 1 not in self.place_hooks else None
             if carried is not None or next_norm is not None:
                 carried = block.forward(step, step.io[place], x, h_in=carried, next_norm=next_norm)
             else:

@@ -52,10 +52,33 @@ _PROTOTYPES = {
         "zlm_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
         "zlm_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float,
                         c_void_p],
-        "zlm_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "zlm_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+        "zlm_rmsnorm_strided": [c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_long, c_int, c_int, c_int, c_float,
+                                c_float, c_void_p],
+        "zlm_add_row": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "zlm_scale": [c_void_p, c_long, c_float, c_void_p],
         "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
         "zlm_convert": [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p],
         "zlm_fill_normal": [c_void_p, c_int, c_long, ctypes.c_ulonglong, c_float, c_float, c_void_p],
+    },
+    "block_linear": {
+        "zlm_block_linear": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_int, c_int,
+                             c_int, c_int, c_int, c_void_p, c_long, c_void_p],
+    },
+    "recurrent": {
+        "zlm_causal_conv": [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int, c_int, c_int, c_void_p],
+        "zlm_gated_scan": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_float,
+                           c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "moe": {
+        "zlm_moe_route": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                          c_void_p],
+        "zlm_moe_max_tiles_scratch": [c_int, c_int],
+        "zlm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "zlm_moe_grouped": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
+                            c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "zlm_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_generic": {
         "zlm_gemm_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -197,18 +220,203 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
            "rmsnorm")
 
 
-def gated_act(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu", interleaved: bool = False) -> None:
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
+
+
+def gated_act(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu", interleaved: bool = False,
+              limit: float = 0.0, slope: float = 1.0) -> None:
     """out[t, j] = act(gate) * up for gu of shape [T, 2I]: gate j, up j in columns (j, I + j), or in columns
-    (2j, 2j + 1) when ``interleaved``."""
+    (2j, 2j + 1) when ``interleaved``.  "swish_clamped": g = min(gate, limit), u = clamp(up, -limit, limit),
+    out = g * sigmoid(slope * g) * (u + 1)."""
     _cuda(gu, "gu"); _cuda(out, "out", gu.dtype)
     T, I = out.shape
     if gu.shape != (T, 2 * I):
         raise KernelError("gated_act: gu must be [T, 2*I]")
-    kind = {"silu": 0, "gelu_tanh": 1}.get(activation)
+    kind = ACTIVATIONS.get(activation)
     if kind is None:
-        raise KernelError(f"gated_act: activation {activation!r} is not known (silu, gelu_tanh)")
+        raise KernelError(f"gated_act: activation {activation!r} is not known ({', '.join(ACTIVATIONS)})")
     _check(_fn("elementwise", "zlm_gated_act")(gu.data_ptr(), out.data_ptr(), code(gu.dtype), T, I, kind,
-                                               int(interleaved), _stream()), "gated_act")
+                                               int(interleaved), float(limit), float(slope), _stream()), "gated_act")
+
+
+def _rows(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be on a CUDA device (there is no CPU path)")
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be a matrix with unit column stride")
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    return t.stride(0) if t.shape[0] > 1 else t.shape[1]
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, add: bool = False,
+                 weight_offset: float = 0.0) -> None:
+    """out[r] = (or += with ``add``) x[r] * rsqrt(mean(x[r]^2) + eps) * (weight + weight_offset).  x is float32;
+    x and out may be column slices of wider matrices (rows with a stride of their own); ``add`` needs a float32
+    out and is how a norm behind a sublayer is summed into the residual stream."""
+    _rows(x, "x"); _rows(out, "out"); _cuda(weight, "weight")
+    n, d = x.shape
+    if x.dtype != torch.float32 or out.shape != (n, d) or weight.numel() != d or (add and out.dtype != torch.float32):
+        raise KernelError("rmsnorm_rows: x must be float32, out of its shape (float32 to add into), weight of its width")
+    _check(_fn("elementwise", "zlm_rmsnorm_strided")(
+        x.data_ptr(), _row_stride(x), weight.data_ptr(), code(weight.dtype), out.data_ptr(), code(out.dtype),
+        _row_stride(out), int(add), n, d, eps, weight_offset, _stream()), "rmsnorm_rows")
+
+
+def add_row(x: torch.Tensor, row: torch.Tensor) -> None:
+    """x[t, :] += row for every t; x is float32 [T, d], row holds d elements."""
+    _cuda(x, "x", torch.float32); _cuda(row, "row")
+    if x.dim() != 2 or row.numel() != x.shape[1]:
+        raise KernelError("add_row: the row must be as wide as x")
+    _check(_fn("elementwise", "zlm_add_row")(x.data_ptr(), row.data_ptr(), code(row.dtype), x.shape[0], x.shape[1],
+                                             _stream()), "add_row")
+
+
+def scale_(x: torch.Tensor, factor: float) -> None:
+    _cuda(x, "x", torch.float32)
+    _check(_fn("elementwise", "zlm_scale")(x.data_ptr(), x.numel(), float(factor), _stream()), "scale_")
+
+
+# ---------------------------------------------------------- block-diagonal product
+BLOCK_EPILOGUES = {None: 0, "sigmoid": 1, "sigmoid_gate": 2}
+
+
+def block_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 epilogue: Optional[str] = None, gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, b*N + n] = epi(sum_k x[t, b*K + k] * w[b, n, k] + bias[b*N + n]) for w of shape [B, N, K]: part b of
+    a row goes through a matrix of its own (a product per attention head, block-diagonal gates).  ``epilogue``:
+    None, "sigmoid", or "sigmoid_gate" (the result times sigmoid(gate[t, b*N + n]), gate float32).  x, out and
+    gate may be column slices of wider matrices.  bias is float32."""
+    _rows(x, "x"); _rows(out, "out"); _cuda(w, "w")
+    if w.dim() != 3:
+        raise KernelError("block_linear: w must be [B, N, K]")
+    B, N, K = w.shape
+    T = x.shape[0]
+    if x.shape[1] != B * K or out.shape != (T, B * N):
+        raise KernelError(f"block_linear: shapes do not match: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32)
+        if bias.numel() != B * N:
+            raise KernelError("block_linear: bias length does not match")
+    if epilogue not in BLOCK_EPILOGUES:
+        raise KernelError(f"block_linear: epilogue {epilogue!r} is not known")
+    gate_stride = 0
+    if epilogue == "sigmoid_gate":
+        if gate is None:
+            raise KernelError("block_linear: the gated epilogue needs a gate")
+        _rows(gate, "gate")
+        if gate.dtype != torch.float32 or gate.shape != (T, B * N):
+            raise KernelError("block_linear: the gate must be float32 of the output's shape")
+        gate_stride = _row_stride(gate)
+    status = _fn("block_linear", "zlm_block_linear")(
+        x.data_ptr(), code(x.dtype), _row_stride(x), w.data_ptr(), code(w.dtype), _ptr(bias), out.data_ptr(),
+        code(out.dtype), _row_stride(out), T, B, N, K, BLOCK_EPILOGUES[epilogue], _ptr(gate), gate_stride, _stream())
+    _check(status, "block_linear")
+
+
+# ------------------------------------------------------------------- recurrence
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, step, u: torch.Tensor) -> None:
+    """u[t, c] = bias[c] + sum_j taps[c, K-1-j] * x[t-j, c] over each sequence of the step; the inputs before the
+    step are rows 0..K-2 of the sequence's state [slots, K, C] (float32; zero for a new sequence).  taps [C, K]
+    and bias [C] are float32; x may be a column slice."""
+    _rows(x, "x"); _cuda(u, "u", x.dtype); _cuda(taps, "taps", torch.float32); _cuda(bias, "bias", torch.float32)
+    _cuda(state, "state", torch.float32)
+    T, C = x.shape
+    K = taps.shape[1]
+    if taps.shape != (C, K) or bias.numel() != C or u.shape != (T, C) or tuple(state.shape[1:]) != (K, C):
+        raise KernelError("causal_conv: shapes do not match")
+    _check(_fn("recurrent", "zlm_causal_conv")(
+        x.data_ptr(), code(x.dtype), _row_stride(x), taps.data_ptr(), bias.data_ptr(), state.data_ptr(), state.stride(0),
+        step.seq_of_token.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), u.data_ptr(), T, C, K,
+        _stream()), "causal_conv")
+
+
+def gated_scan(u: torch.Tensor, gates: torch.Tensor, gate_block: int, y: torch.Tensor, x: torch.Tensor,
+               lam: torch.Tensor, rate: float, state: torch.Tensor, step, out: torch.Tensor) -> None:
+    """The recurrence S_t = a_t S_{t-1} + sqrt(1 - a_t^2) i_t u_t with a_t = exp(-rate r_t softplus(lam)), carried in
+    row K-1 of the sequence's state, out_t = S_t * gelu_tanh(y_t); it also leaves the last K-1 rows of x (the
+    convolution's inputs) in rows 0..K-2 of the state.  gates: float32 [T, 2C], per block of ``gate_block``
+    channels first r then i."""
+    _cuda(u, "u"); _cuda(out, "out", u.dtype); _cuda(gates, "gates", torch.float32); _cuda(lam, "lam", torch.float32)
+    _rows(y, "y"); _rows(x, "x"); _cuda(state, "state", torch.float32)
+    T, C = u.shape
+    K = state.shape[1]
+    if (gates.shape != (T, 2 * C) or y.shape != (T, C) or x.shape != (T, C) or out.shape != (T, C) or lam.numel() != C
+            or state.shape[2] != C or y.dtype != u.dtype or x.dtype != u.dtype):
+        raise KernelError("gated_scan: shapes or types do not match")
+    _check(_fn("recurrent", "zlm_gated_scan")(
+        u.data_ptr(), code(u.dtype), gates.data_ptr(), int(gate_block), y.data_ptr(), _row_stride(y), x.data_ptr(),
+        _row_stride(x), lam.data_ptr(), float(rate), state.data_ptr(), state.stride(0), step.cu_seqlens.data_ptr(),
+        step.slots.data_ptr(), out.data_ptr(), step.n_seqs, step.max_new, C, K, _stream()), "gated_scan")
+
+
+# ------------------------------------------------------------ mixture of experts
+def moe_route(z: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int, keep_groups: int,
+              group_best: int, ids: torch.Tensor, weights: torch.Tensor, softmax_scores: bool = False,
+              renormalize: bool = False) -> None:
+    """Per token: scores = sigmoid(z) (or softmax), chosen by score + correction within the ``keep_groups`` groups
+    whose ``group_best`` best choice scores sum highest; ids int32 [T, top], weights float32 [T, top] (the scores
+    of the chosen, divided by their sum with ``renormalize``)."""
+    _cuda(z, "z", torch.float32); _cuda(ids, "ids", torch.int32); _cuda(weights, "weights", torch.float32)
+    T, E = z.shape
+    if correction is not None:
+        _cuda(correction, "correction", torch.float32)
+        if correction.numel() != E:
+            raise KernelError("moe_route: one correction per expert is needed")
+    if ids.shape != (T, top) or weights.shape != (T, top):
+        raise KernelError("moe_route: ids and weights must be [T, top]")
+    _check(_fn("moe", "zlm_moe_route")(z.data_ptr(), _ptr(correction), T, E, top, n_groups, keep_groups, group_best,
+                                       int(softmax_scores), int(renormalize), ids.data_ptr(), weights.data_ptr(),
+                                       _stream()), "moe_route")
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+    return int(_fn("moe", "zlm_moe_max_tiles_scratch")(n_pairs, n_experts))
+
+
+def moe_group(ids: torch.Tensor, n_experts: int, offs: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor,
+              tile_row: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """Group the (token, choice) pairs by expert: ``order`` lists the pairs expert by expert, ``offs`` [E + 1] where
+    each expert's run starts, and the runs are cut into tiles of rows for the grouped products."""
+    for t, n in ((ids, "ids"), (offs, "offs"), (order, "order"), (tile_expert, "tile_expert"), (tile_row, "tile_row"),
+                 (n_tiles, "n_tiles")):
+        _cuda(t, n, torch.int32)
+    P = ids.numel()
+    need = moe_max_tiles(P, n_experts)
+    if offs.numel() < n_experts + 1 or order.numel() < P or tile_expert.numel() < need or tile_row.numel() < need:
+        raise KernelError("moe_group: an output is too short")
+    _check(_fn("moe", "zlm_moe_group")(ids.data_ptr(), P, n_experts, offs.data_ptr(), order.data_ptr(),
+                                       tile_expert.data_ptr(), tile_row.data_ptr(), n_tiles.data_ptr(), _stream()),
+           "moe_group")
+
+
+def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, glu: bool, n_pairs: int, top: int,
+                offs: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor, tile_row: torch.Tensor,
+                n_tiles: torch.Tensor) -> None:
+    """The experts' products over the grouped pairs.  ``glu``: x [T, K] by token, w [E, 2N, K] (gate rows, then up
+    rows), out [P, N] = silu(gate) * up in x's type, rows in grouped order.  Otherwise: x [P, K] in grouped order,
+    w [E, N, K], out float32 [P, N] with row p the result of pair p."""
+    _rows(x, "x"); _cuda(w, "w"); _rows(out, "out")
+    E, NW, K = w.shape
+    N = NW // 2 if glu else NW
+    if x.shape[1] != K or out.shape != (n_pairs, N) or out.dtype != (x.dtype if glu else torch.float32):
+        raise KernelError("moe_grouped: shapes or types do not match")
+    _check(_fn("moe", "zlm_moe_grouped")(
+        x.data_ptr(), code(x.dtype), _row_stride(x), w.data_ptr(), code(w.dtype), out.data_ptr(), _row_stride(out),
+        int(glu), n_pairs, E, N, K, top, offs.data_ptr(), order.data_ptr(), tile_expert.data_ptr(), tile_row.data_ptr(),
+        n_tiles.data_ptr(), _stream()), "moe_grouped")
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, accumulate: bool) -> None:
+    """out[t] (+)= sum_k weights[t, k] * y[t * top + k], k ascending; all float32."""
+    _cuda(y, "y", torch.float32); _cuda(weights, "weights", torch.float32); _cuda(out, "out", torch.float32)
+    T, top = weights.shape
+    d = out.shape[1]
+    if y.shape != (T * top, d) or out.shape[0] != T:
+        raise KernelError("moe_combine: shapes do not match")
+    _check(_fn("moe", "zlm_moe_combine")(y.data_ptr(), weights.data_ptr(), out.data_ptr(), T, d, top, int(accumulate),
+                                         _stream()), "moe_combine")
 
 
 def add_(y: torch.Tensor, x: torch.Tensor) -> None:
@@ -265,16 +473,19 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
 def rope_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary_dim: int,
                inv_freq: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor,
                block_table: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-               page_size: int) -> None:
+               page_size: int, keys_only: bool = False) -> None:
     """Rotate q and k of qkv[T, (n_heads+2 n_kv) head_dim] in place and store k, v in the cache pages.
 
-    k_pages / v_pages: [n_pages, n_kv, page_size, head_dim] of one layer, or None to store nothing.
+    k_pages / v_pages: [n_pages, n_kv, page_size, head_dim] of one layer, or None to store nothing.  With
+    ``keys_only`` the rows are [q heads | k heads] and only the keys are stored (``v_pages`` is not touched).
     block_table: int32 [B, stride]; row seq_of_token[t] lists the pages of token t's sequence.
     """
     _cuda(qkv, "qkv"); _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
     _cuda(block_table, "block_table", torch.int32)
     T = qkv.shape[0]
-    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+    if keys_only:
+        v_pages = None
+    if qkv.shape[1] != (n_heads + (1 if keys_only else 2) * n_kv) * head_dim:
         raise KernelError("rope_store: qkv width does not match the head counts")
     if inv_freq is not None:
         _cuda(inv_freq, "inv_freq", torch.float32)
@@ -282,8 +493,12 @@ def rope_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary
             raise KernelError("rope_store: the frequency table must hold rotary_dim/2 entries")
     page_stride = 0
     if k_pages is not None:
-        _cuda(k_pages, "k_pages", qkv.dtype); _cuda(v_pages, "v_pages", qkv.dtype)
-        if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        _cuda(k_pages, "k_pages", qkv.dtype)
+        if v_pages is not None:
+            _cuda(v_pages, "v_pages", qkv.dtype)
+        elif not keys_only:
+            raise KernelError("rope_store: value pages are needed unless only keys are stored")
+        if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or (v_pages is not None and k_pages.shape != v_pages.shape):
             raise KernelError("rope_store: cache pages must be [n_pages, n_kv, page_size, head_dim]")
         page_stride = k_pages.stride(0)
     _check(_fn("attention", "zlm_rope_store")(
@@ -317,8 +532,8 @@ def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: 
     T = out.shape[0]
     if out.shape[1] != n_heads * head_dim or qkv.shape[1] < n_heads * head_dim:
         raise KernelError("attention: widths do not match the head counts")
-    if head_dim % 8 or head_dim > 256:
-        raise KernelError(f"attention: head size {head_dim} is not supported (a multiple of 8, at most 256)")
+    if head_dim % 8 or head_dim > 512:
+        raise KernelError(f"attention: head size {head_dim} is not supported (a multiple of 8, at most 512)")
     if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
         raise KernelError("attention: cache pages must be [n_pages, n_kv, page_size, head_dim]")
     _check(_fn("attention", "zlm_attention_general")(

@@ -52,10 +52,13 @@ class ParamDecl:
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values a mixer wants kept: per position n_kv_heads x head_dim, all of them or a window."""
+    """Keys and values a mixer wants kept: per position n_kv_heads x head_dim, all of them or a window.
+    ``values_are_keys``: one vector per position serves as key and as value (a latent both are made from), so
+    only the key pages exist and ``LayerIO.v_pages`` is the same memory."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values_are_keys: bool = False
 
 
 @dataclass(frozen=True)
@@ -91,6 +94,7 @@ class Part:
     fuses_next_norm = False
     takes_normed_input = False
     fusable = False
+    can_overwrite = False      # mixers and feed-forwards: ``forward(..., accumulate=False)`` writes instead of adding
 
     def __init__(self, spec: Any, dtype: torch.dtype, device: torch.device):
         self.spec = spec

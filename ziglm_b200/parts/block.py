@@ -78,3 +78,94 @@ class PreNormBlock(Part):
 
 
 register_block("prenorm", PreNormBlock)
+
+
+class SandwichBlock(Part):
+    """Norms before and after each sublayer: x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x))).
+
+    The two post-norms come in ``LayerSpec.options`` (``mixer_post_norm``, ``ffn_post_norm``); a layer whose spec
+    has no feed-forward (``ffn`` and ``ffn_norm`` are None) ends after the mixer.  A sublayer writes its output
+    into a float32 branch buffer of the step's scratch (a part that sets ``can_overwrite`` is asked to overwrite
+    it, for any other the buffer is zeroed first and the part adds into it, as it would into the residual); the
+    post-norm then reads the branch in float32 and adds the normed rows into the residual in the same kernel.
+    """
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        self.parts: Dict[str, Part] = {}
+        for prefix, klass, sub in self._children(spec):
+            self.parts[prefix] = klass(sub, dtype, device)
+        self.mixer_norm = self.parts["mixer_norm."]
+        self.mixer = self.parts["mixer."]
+        self.mixer_post = self.parts["mixer_post_norm."]
+        self.ffn_norm = self.parts.get("ffn_norm.")
+        self.ffn = self.parts.get("ffn.")
+        self.ffn_post = self.parts.get("ffn_post_norm.")
+
+    @classmethod
+    def _children(cls, spec: LayerSpec):
+        post = spec.options["mixer_post_norm"]
+        out = [("mixer_norm.", norm_class(spec.mixer_norm.kind), spec.mixer_norm),
+               ("mixer.", mixer_class(spec.mixer.kind), spec.mixer),
+               ("mixer_post_norm.", norm_class(post.kind), post)]
+        if spec.ffn is not None:
+            post = spec.options["ffn_post_norm"]
+            out += [("ffn_norm.", norm_class(spec.ffn_norm.kind), spec.ffn_norm),
+                    ("ffn.", feed_forward_class(spec.ffn.kind), spec.ffn),
+                    ("ffn_post_norm.", norm_class(post.kind), post)]
+        return out
+
+    @classmethod
+    def declare(cls, spec: LayerSpec) -> Dict[str, ParamDecl]:
+        out: Dict[str, ParamDecl] = {}
+        for prefix, klass, sub in cls._children(spec):
+            for name, decl in klass.declare(sub).items():
+                out[prefix + name] = decl
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for prefix, part in self.parts.items():
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        libs: Tuple[str, ...] = ()
+        for part in self.parts.values():
+            libs += part.kernel_libraries()
+        return libs
+
+    def cache_needs(self) -> Optional[KVNeed]:
+        return self.mixer.cache_needs()
+
+    def state_needs(self) -> Optional[StateNeed]:
+        return self.mixer.state_needs()
+
+    def accepts_normed_input(self) -> bool:
+        return False
+
+    @staticmethod
+    def _branch(step, part, x: torch.Tensor) -> torch.Tensor:
+        branch = step.ws.buf("branch", tuple(x.shape), torch.float32)
+        if not part.can_overwrite:
+            branch.zero_()
+        return branch
+
+    def forward(self, step, io: LayerIO, x: torch.Tensor, h_in=None, next_norm=None):
+        h = self.mixer_norm.forward(step, x)
+        branch = self._branch(step, self.mixer, x)
+        if self.mixer.can_overwrite:
+            self.mixer.forward(step, io, h, branch, accumulate=False)
+        else:
+            self.mixer.forward(step, io, h, branch)
+        self.mixer_post.add_normed(step, branch, x)
+        if self.ffn is not None:
+            h = self.ffn_norm.forward(step, x)
+            branch = self._branch(step, self.ffn, x)
+            if self.ffn.can_overwrite:
+                self.ffn.forward(step, h, branch, accumulate=False)
+            else:
+                self.ffn.forward(step, h, branch)
+            self.ffn_post.add_normed(step, branch, x)
+        return None
+
+
+register_block("sandwich", SandwichBlock)

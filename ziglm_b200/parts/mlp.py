@@ -25,8 +25,13 @@ from .linear import Linear
 class GatedMLP(Part):
     def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device: torch.device):
         super().__init__(spec, dtype, device)
-        if spec.activation not in ("silu", "gelu_tanh"):
-            raise ValueError(f"gated_mlp: activation {spec.activation!r} is not known (silu, gelu_tanh)")
+        if spec.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation {spec.activation!r} is not known ({', '.join(kernels.ACTIVATIONS)})")
+        # "swish_clamped": gate and up are clamped to a limit and the gate's sigmoid has a slope (both in options)
+        self.limit = float(spec.options.get("limit", 0.0))
+        self.slope = float(spec.options.get("slope", 1.0))
+        if spec.activation == "swish_clamped" and not self.limit > 0.0:
+            raise ValueError("gated_mlp: the clamped activation needs a positive limit")
         self.intermediate = spec.intermediate
         self.interleaved = False
         self.gate_up: Optional[Linear] = None
@@ -68,21 +73,27 @@ class GatedMLP(Part):
 
     fuses_next_norm = True
     takes_normed_input = True
+    can_overwrite = True
 
-    def forward(self, step, h, residual: torch.Tensor, next_norm=None):
+    def forward(self, step, h, residual: torch.Tensor, next_norm=None, accumulate: bool = True):
         """``h``: the normalised rows or a half-done norm (:class:`NormedInput`).  With ``next_norm`` the down
-        projection may do the first half of that norm; the result is then its :class:`NormedInput`."""
+        projection may do the first half of that norm; the result is then its :class:`NormedInput`.
+        ``accumulate=False``: the result overwrites ``residual`` (a branch buffer) instead of adding to it."""
         T = residual.shape[0]
         act = step.ws.buf("ffn_act", (T, self.intermediate), self.dtype)
         normed = isinstance(h, NormedInput)
         rows = h.hb if normed else h
-        fused = self.interleaved and kernels.gemm_tc(rows, self.gate_up.weight, act, bias=self.gate_up.bias,
-                                                     glu=self.spec.activation,
-                                                     row_scale=(h.ssq, h.eps) if normed else None)
+        fused = (self.interleaved and self.spec.activation in kernels.GLU_KINDS
+                 and kernels.gemm_tc(rows, self.gate_up.weight, act, bias=self.gate_up.bias, glu=self.spec.activation,
+                                     row_scale=(h.ssq, h.eps) if normed else None))
         if not fused:
             gu = step.ws.buf("gate_up", (T, 2 * self.intermediate), self.dtype)
             self.gate_up(h, gu)
-            kernels.gated_act(gu, act, self.spec.activation, interleaved=self.interleaved)
+            kernels.gated_act(gu, act, self.spec.activation, interleaved=self.interleaved, limit=self.limit,
+                              slope=self.slope)
+        if not accumulate:
+            self.down(act, residual)
+            return None
         return self.down.accumulate_with_norm(step, act, residual, next_norm, "ffn_next")
 
 

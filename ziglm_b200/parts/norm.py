@@ -45,5 +45,15 @@ class RMSNorm(Part):
         kernels.rmsnorm(x, self.weight, out, self.eps, rows=rows, weight_offset=self.weight_offset)
         return out
 
+    def add_normed(self, step, branch: torch.Tensor, residual: torch.Tensor) -> None:
+        """residual += norm(branch), both float32 [T, width]: a norm behind a sublayer, summed into the residual
+        stream by the kernel that takes it."""
+        kernels.rmsnorm_rows(branch, self.weight, residual, self.eps, add=True, weight_offset=self.weight_offset)
+
+    def forward_rows(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """The norm of float32 rows that may be a column slice of a wider matrix, into rows that may be one too."""
+        kernels.rmsnorm_rows(x, self.weight, out, self.eps, weight_offset=self.weight_offset)
+        return out
+
 
 register_norm("rmsnorm", RMSNorm)
