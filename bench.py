@@ -396,6 +396,163 @@ def run_case(args):
     return 0
 
 
+def _timed(fn, warmup, steps, flush):
+    """Median device time (ms) of ``fn()``, with a buffer larger than L2 rewritten before every timed call."""
+    import torch
+    times = []
+    for k in range(warmup + steps):
+        flush.add_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        if k >= warmup:
+            times.append(s.elapsed_time(e))
+    return sorted(times)[len(times) // 2]
+
+
+def run_tumatar(args):
+    """The Tumatar design beside the Llama shape of the same width, with random weights: a prompt of
+    ``--prompt-tokens`` and decode steps of ``--batch`` sequences at ``--context``, ``--layers`` layer runs of each
+    (default 4), and every kernel the design adds, alone, against its own roofline (the larger of bytes / measured
+    copy bandwidth and FLOPs / measured bf16 peak), beside the library's kernels of the like kind."""
+    import torch
+    from types import SimpleNamespace
+    from ziglm_b200 import kernels
+    from ziglm_b200.config.shapes import shape
+    torch.cuda.set_device(0)
+    pk = peaks()
+    size = "8b" if args.shape == "8b" else "1b"
+    layers = args.layers or 4
+    T, batch, context = args.prompt_tokens, args.batch, args.context
+    max_seq = max(context, T) + 64
+    gen = torch.Generator().manual_seed(7)
+    out = {"case": "tumatar", "width_of": "llama-" + size, "dtype": "bf16", "layer_runs": layers, "prompt_tokens": T,
+           "batch": batch, "context": context, "data": "synthetic", "l2": "a 256 MiB buffer is rewritten before every timed call",
+           "peaks": pk["source"], "models": {}}
+    for name in ("tumatar-" + size, "llama-" + size):
+        cfg = shape(name)
+        if "layers" in cfg:
+            cfg["layers"] = cfg["layers"][:layers]
+            vocab = cfg["vocab"]
+        else:
+            cfg["num_hidden_layers"] = layers
+            cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], max_seq)
+            vocab = cfg["vocab_size"]
+        eng = _engine_for(cfg, "bfloat16", batch, max_seq)
+        ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        pre = _time_prompt(eng, ids(T), args.warmup, args.steps)
+        dec = _time_decode_at(eng, batch, context, args.warmup, args.steps, ids)
+        out["models"][name] = {"prefill_ms": round(pre, 3), "prefill_tok_s": round(T / pre * 1e3, 1),
+                               "decode_ms": round(dec, 4), "decode_tok_s": round(batch / dec * 1e3, 1)}
+        del eng
+        torch.cuda.empty_cache()
+    # ---- the kernels, alone
+    cfg = shape("tumatar-" + size)
+    d = cfg["width"]
+    lat, rec = cfg["layers"][1]["mixer"], cfg["layers"][0]["mixer"]
+    moe = cfg["layers"][1]["mlp"]
+    H, D, R, C, K = lat["heads"], lat["dim"], lat["kv_rank"], rec["width"], rec["conv"]
+    nb = rec["blocks"]
+    E, top, ff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"]
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    bf = lambda *sh: (torch.randn(*sh, device=dev) * 0.05).to(torch.bfloat16)
+    f32 = lambda *sh: torch.randn(*sh, device=dev) * 0.05
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = []
+
+    def report(what, like, ms, nbytes, flops):
+        floor = max(nbytes / hbm, flops / peak) * 1e3
+        rows.append({"kernel": what, "like": like, "ms": round(ms, 4), "roofline_ms": round(floor, 4),
+                     "frac_of_roofline": round(floor / ms, 4)})
+
+    kernels.require(("elementwise", "block_linear", "recurrent", "moe", "gemm_generic", "gemm_tc"))
+    for n_tok, tag in ((T, f"prompt of {T}"), (batch, f"decode batch {batch}")):
+        st = SimpleNamespace(seq_of_token=torch.zeros(n_tok, dtype=torch.int32, device=dev) if n_tok == T else
+                             torch.arange(n_tok, dtype=torch.int32, device=dev),
+                             cu_seqlens=(torch.tensor([0, n_tok], dtype=torch.int32, device=dev) if n_tok == T else
+                                         torch.arange(n_tok + 1, dtype=torch.int32, device=dev)),
+                             slots=torch.arange(1 if n_tok == T else n_tok, dtype=torch.int32, device=dev),
+                             n_seqs=1 if n_tok == T else n_tok, max_new=n_tok if n_tok == T else 1, n_tokens=n_tok)
+        # the library's like kernels at the same width: a dense product, a norm
+        x, w, y = bf(n_tok, d), bf(d, d), torch.empty(n_tok, d, dtype=torch.bfloat16, device=dev)
+        ms = _timed(lambda: kernels.gemm_tc(x, w, y), args.warmup, args.steps, flush)
+        report(f"gemm_tc {d}x{d}, {tag}", "-", ms, 2 * (n_tok * d * 2) + d * d * 2, 2.0 * n_tok * d * d)
+        xr, wn, yn = f32(n_tok, d), bf(d), torch.empty(n_tok, d, dtype=torch.bfloat16, device=dev)
+        ms = _timed(lambda: kernels.rmsnorm(xr, wn, yn, 1e-6), args.warmup, args.steps, flush)
+        report(f"rmsnorm, {tag}", "-", ms, n_tok * d * 6 + d * 2, 0)
+        # the design's own
+        res = f32(n_tok, d)
+        ms = _timed(lambda: kernels.rmsnorm_rows(xr, wn, res, 1e-6, add=True), args.warmup, args.steps, flush)
+        report(f"rmsnorm_rows (post-norm + residual sum), {tag}", "rmsnorm", ms, n_tok * d * 12 + d * 2, 0)
+        q, ukt = bf(n_tok, H * D), bf(H, R, D)
+        qc = torch.empty(n_tok, (H + 1) * R, dtype=torch.bfloat16, device=dev)
+        ms = _timed(lambda: kernels.block_linear(q, ukt, qc[:, :H * R]), args.warmup, args.steps, flush)
+        report(f"block_linear (queries into the latent, {H} heads {D}->{R}), {tag}", "gemm_tc", ms,
+               n_tok * H * (D + R) * 2 + H * R * D * 2, 2.0 * n_tok * H * D * R)
+        u, gw, gb = bf(n_tok, C), bf(nb, 2 * C // nb, C // nb), f32(2 * C)
+        gates = torch.empty(n_tok, 2 * C, dtype=torch.float32, device=dev)
+        ms = _timed(lambda: kernels.block_linear(u, gw, gates, bias=gb, epilogue="sigmoid"), args.warmup, args.steps, flush)
+        report(f"block_linear (gates of the recurrence, {nb} blocks of {C // nb}), {tag}", "gemm_tc", ms,
+               n_tok * C * 2 + n_tok * 2 * C * 4 + gw.numel() * 2, 2.0 * n_tok * 2 * C * (C // nb))
+        proj, taps, cb, lam = bf(n_tok, 2 * C), f32(C, K), f32(C), f32(C)
+        state = torch.zeros(st.n_seqs, K, C, device=dev)
+        uo = torch.empty(n_tok, C, dtype=torch.bfloat16, device=dev)
+        ms = _timed(lambda: kernels.causal_conv(proj[:, C:], taps, cb, state, st, uo), args.warmup, args.steps, flush)
+        report(f"causal_conv ({K} taps), {tag}", "rmsnorm", ms, n_tok * C * 4, 0)
+        gates.uniform_(0.1, 0.9)
+        so = torch.empty_like(uo)
+        ms = _timed(lambda: kernels.gated_scan(uo, gates, C // nb, proj[:, :C], proj[:, C:], lam, 8.0, state, st, so),
+                    args.warmup, args.steps, flush)
+        report(f"gated_scan, {tag}", "rmsnorm", ms, n_tok * C * (2 + 8 + 2 + 2), 0)
+        # the experts: routing, grouping, the two grouped products, the sum
+        P = n_tok * top
+        h, z = bf(n_tok, d), f32(n_tok, E) * 40
+        ids = torch.empty(n_tok, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(n_tok, top, dtype=torch.float32, device=dev)
+        corr = f32(E)
+        ms = _timed(lambda: kernels.moe_route(z, corr, top, 4, 2, 2, ids, wts), args.warmup, args.steps, flush)
+        report(f"moe_route ({E} experts), {tag}", "rmsnorm", ms, n_tok * (E * 4 + top * 8), 0)
+        mt = kernels.moe_max_tiles(P, E)
+        i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
+        offs, order, place, te, tr, nt = i32(E + 1), i32(P), i32(P), i32(mt), i32(mt), i32(1)
+        grp = (offs, order, te, tr, nt)
+        ms = _timed(lambda: kernels.moe_group(ids.view(-1), E, offs, order, place, te, tr, nt), args.warmup, args.steps, flush)
+        report(f"moe_group, {tag}", "-", ms, P * 12, 0)
+        wgu, wd = bf(E, 2 * ff, d), bf(E, d, ff)
+        act = torch.empty(P, ff, dtype=torch.bfloat16, device=dev)
+        yy = torch.empty(P, d, dtype=torch.float32, device=dev)
+        used = min(E, P)
+        gu_bytes, gu_flops = used * 2 * ff * d * 2 + P * d * 2 + P * ff * 2, 2.0 * P * 2 * ff * d
+        dn_bytes, dn_flops = used * ff * d * 2 + P * ff * 2 + P * d * 4, 2.0 * P * ff * d
+        if n_tok >= 128:
+            import ctypes
+            hrows = torch.empty(P, d, dtype=torch.bfloat16, device=dev)
+            ms = _timed(lambda: kernels.moe_gather(h, order, top, hrows), args.warmup, args.steps, flush)
+            report(f"moe_gather, {tag}", "rmsnorm", ms, P * d * 4, 0)
+            host_offs = offs.cpu()
+            hp = ctypes.c_void_p(host_offs.data_ptr())
+            ms = _timed(lambda: kernels.gemm_tc_groups(hrows, wgu, act, hp, glu="silu"), args.warmup, args.steps, flush)
+            report(f"gemm_tc per expert, gate/up ({ff} per expert, {E} launches), {tag}", "gemm_tc (gated)", ms, gu_bytes, gu_flops)
+            ms = _timed(lambda: kernels.gemm_tc_groups(act, wd, yy, hp), args.warmup, args.steps, flush)
+            report(f"gemm_tc per expert, down ({E} launches), {tag}", "gemm_tc", ms, dn_bytes, dn_flops)
+        else:
+            ms = _timed(lambda: kernels.moe_grouped(h, wgu, act, True, P, top, *grp, interleaved=True, skinny=True),
+                        args.warmup, args.steps, flush)
+            report(f"moe_grouped gate/up, streaming ({ff} per expert), {tag}", "gemm_tc (gated)", ms, gu_bytes, gu_flops)
+            ms = _timed(lambda: kernels.moe_grouped(act, wd, yy, False, P, top, *grp, skinny=True), args.warmup, args.steps, flush)
+            report(f"moe_grouped down, streaming, {tag}", "gemm_tc", ms, dn_bytes, dn_flops)
+        ms = _timed(lambda: kernels.moe_combine(yy, wts, res, True), args.warmup, args.steps, flush)
+        report(f"moe_combine, {tag}", "rmsnorm", ms, P * d * 4 + n_tok * d * 8, 0)
+    out["kernels"] = rows
+    out["wait_errors"] = wait_errors(kernels)
+    print(json.dumps(out))
+    return 0
+
+
 def run_workload(args):
     """The two workloads beside the headline one, through ``Engine.generate`` (host token ids in, ids out):
 
@@ -614,10 +771,12 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--case", default="full",
-                    choices=["full", "prefill", "decode", "workload-1b", "workload-13b", "float32", "reference-kernels"],
+                    choices=["full", "prefill", "decode", "workload-1b", "workload-13b", "float32", "reference-kernels",
+                             "tumatar"],
                     help="full: the whole measurement; prefill / decode: that phase alone (for profilers and sweeps); "
                          "workload-1b / workload-13b: the two other workloads through Engine.generate; float32: the "
-                         "8B shape in true 32-bit; reference-kernels: the reference's CUDA kernels alone, if built")
+                         "8B shape in true 32-bit; reference-kernels: the reference's CUDA kernels alone, if built; tumatar: the "
+                         "Tumatar design beside the Llama shape of the same width (--shape 1b or 8b), and its kernels alone")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="--case prefill/decode: layer sizes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="--case prefill/decode")
     ap.add_argument("--repeats", type=int, default=2, help="workload cases: timed repetitions after one warm-up")
@@ -639,6 +798,8 @@ def main():
         return run_workload(args)
     if args.case == "float32":
         return run_float32(args)
+    if args.case == "tumatar":
+        return run_tumatar(args)
     if args.case != "full":
         return run_case(args)
     return run_ours(args)

@@ -22,7 +22,7 @@ def test_layout_of_a_repeated_run():
     assert [(li, t) for li, t in conf.running_order()] == [(li, t) for li, t in P.running_order(TC.config("A"))]
     decl = declare_parameters(spec)
     assert decl["loop.step"].shape == (2, 96) and decl["embed"].shape == (211, 96) and decl["final.norm"].shape == (96,)
-    assert decl["l0.mix.uk"].shape == (72, 48) and decl["l0.mix.uv"].shape == (48, 48) and decl["l0.mix.g"].shape == (48, 96)
+    assert decl["l0.mix.uk"].shape == (72, 44) and decl["l0.mix.uv"].shape == (48, 44) and decl["l0.mix.g"].shape == (48, 96)
     assert decl["l0.mix.dq.norm"].shape == (40,) and decl["l0.mlp.correction"].shape == (8,)
     assert decl["l0.mlp.e7.down"].shape == (96, 40) and "l0.mlp.e8.down" not in decl
     assert decl["l1.mix.ra"].shape == (4, 16, 16) and decl["l1.mix.conv"].shape == (64, 3) and decl["l1.mix.lam"].shape == (64,)

@@ -1,8 +1,8 @@
 """Small Tumatar configurations for the tests, and how a model with tensors the test controls is built.
 
 The configurations differ from one another in every size and option: heads that share nothing with powers of
-two, value sizes other than the key size, latents of 48, 64, 128 and 320 elements (64 and 128 are what the
-tensor-core attention takes in bfloat16; 320 is above the 256 of a usual head), a recurrence with one block
+two, value sizes other than the key size, latents of 44, 64, 128 and 320 elements (64 and 128 are what the
+tensor-core attention takes in bfloat16; 320 is above the 256 of a usual head; 44 is no multiple of 8), a recurrence with one block
 and one tap (sizes that make parts of the formulas trivial), layers without a feed-forward, experts without
 groups, a repeated run of layers, and none.
 """
@@ -28,7 +28,7 @@ CFG_A = {
     "architecture": "Tumatar", "vocab": 211, "width": 96, "embedding": {"scale": 3.0}, "norm": {"eps": 1e-5},
     "logit_scale": 0.5, "loop": {"start": 1, "stop": 3, "times": 2},
     "layers": [
-        {"type": "latent_attention", "mixer": _lat(3, 24, 16, 40, 48, 0.2), "mlp": _moe(40, 8, 2, 4, 2)},
+        {"type": "latent_attention", "mixer": _lat(3, 24, 16, 40, 44, 0.2), "mlp": _moe(40, 8, 2, 4, 2)},
         {"type": "rglru", "mixer": {"width": 64, "blocks": 4, "conv": 3}, "mlp": None},
         {"type": "latent_attention", "mixer": _lat(4, 16, 32, 24, 64, 0.25),
          "mlp": {"kind": "dense", "ff": 136, "limit": 0.75}},
@@ -108,7 +108,7 @@ def build(cfg: dict, seed: int, dn: str, tweak: Optional[Callable] = long_memory
 
 def rows_close(got: torch.Tensor, want: torch.Tensor, dn: str, what: str = "") -> None:
     """Row by row: the difference of the logits (mean taken off, root mean square over the vocabulary) relative
-    to the root mean square of the row.  float32: every row within 3e-5.  bfloat16: all rows but one in fifty
+    to the root mean square of the row.  float32: every row within 3e-5.  bfloat16: all rows but one in twenty-five (or two)
     within 0.04 (a router's close call may send a token to another expert, which with one expert a token changes
     the whole feed-forward's output), and those within 1."""
     got = got.detach().float().cpu()
@@ -123,5 +123,5 @@ def rows_close(got: torch.Tensor, want: torch.Tensor, dn: str, what: str = "") -
         assert err.max().item() < 3e-5, f"{what}: row {int(err.argmax())} differs by {err.max().item():.3g}"
     else:
         over = int((err > 0.04).sum())
-        assert err.max().item() < 1.0 and over <= max(1, got.shape[0] // 50), \
+        assert err.max().item() < 1.0 and over <= max(2, got.shape[0] // 25), \
             f"{what}: {over} of {got.shape[0]} rows differ, the worst (row {int(err.argmax())}) by {err.max().item():.3g}"

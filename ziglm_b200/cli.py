@@ -4,7 +4,7 @@
     ziglm bench -m <model_folder> [-n N] [--batch B] [--prompt-len L]
     ziglm test-model --create-sample <folder>
 
-``-m synthetic:<shape>`` (tiny, llama-1b, llama-8b, llama-13b, or the path of a config.json) runs a model whose
+``-m synthetic:<shape>`` (tiny, llama-1b, llama-8b, llama-13b, tumatar-1b, tumatar-8b, or the path of a config.json) runs a model whose
 weights are filled from ``--seed`` on the device, with no folder (``--layers L`` keeps the first L layers).
 
 Option names, defaults and meanings are the reference's (src/cli.zig:67-149): ``-m/--model``,
@@ -87,8 +87,13 @@ def _engine(args):
                 cfg = json.load(f)
         else:
             raise SystemExit(f"synthetic:{name}: not a known shape ({', '.join(sorted(SHAPES))}) nor a config.json")
-        if args.layers:
+        if args.layers and "num_hidden_layers" in cfg:
             cfg["num_hidden_layers"] = min(args.layers, cfg["num_hidden_layers"])
+        elif args.layers and isinstance(cfg.get("layers"), list):
+            cfg["layers"] = cfg["layers"][:args.layers]           # a design that lists its layers
+            loop = cfg.get("loop")
+            if loop and loop.get("stop", 0) > len(cfg["layers"]):
+                cfg["loop"] = None
     else:
         cfg = read_config_json(args.model_path)
     limit = int(cfg.get("max_position_embeddings") or args.max_seq_len)

@@ -48,6 +48,26 @@ SHAPES: Dict[str, Dict[str, Any]] = {
 }
 
 
+def _tumatar(width: int, vocab: int, pairs: int, heads: int, ff: int, experts: int, expert_ff: int) -> Dict[str, Any]:
+    """A Tumatar stack of ``pairs`` times (recurrence + dense feed-forward, latent attention + experts) at the
+    width of a Llama shape: heads of 128 with a key/value latent of 128 (what the tensor-core attention takes),
+    a query latent of three eighths of the width, a recurrence as wide as the model in blocks of 128 channels."""
+    rec = {"type": "rglru", "mixer": {"width": width, "blocks": width // 128, "conv": 4},
+           "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+    att = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": 128, "vdim": 128, "q_rank": 3 * width // 8, "kv_rank": 128, "scale": 128 ** -0.5},
+           "mlp": {"kind": "moe", "expert": {"ff": expert_ff},
+                   "router": {"experts": experts, "top": 2, "groups": {"count": 4, "keep": 2}}}}
+    return {"architecture": "Tumatar", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "logit_scale": 1.0, "loop": None,
+            "layers": [copy.deepcopy(x) for _ in range(pairs) for x in (rec, att)]}
+
+
+# the new design at the widths of the 1B and 8B Llama shapes (as many layer runs, the same vocabulary)
+SHAPES["tumatar-1b"] = _tumatar(2048, 128256, 8, 16, 8192, 16, 2048)
+SHAPES["tumatar-8b"] = _tumatar(4096, 128256, 16, 32, 14336, 16, 3584)
+
+
 def shape(name: str) -> Dict[str, Any]:
     """A copy of the named config.json dictionary."""
     try:

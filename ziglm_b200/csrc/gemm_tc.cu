@@ -57,6 +57,8 @@ struct TcArgs {
     int grid_x;          // blocks (clusters when K is split) that share the tiles
     int tma_store;       // the output goes through shared memory and a TMA store / reduce
     int glu_kind;        // gated mode: 0 silu, 1 tanh gelu
+    float glu_limit;     // gated mode, silu: > 0 makes it the clamped swish min(g, L) sigmoid(slope min(g, L)) (clamp(u, -L, L) + 1)
+    float glu_slope;
     // RMSNorm split over two products (steps of a few tokens, see zlm_gemm_tc_norm):
     // this product finishes the residual sum and leaves x * gain as bf16 and the sums of squares per tile row
     const void* norm_gain;      // [N] gain of the norm that follows, or null
@@ -103,6 +105,18 @@ __device__ __forceinline__ float gated_activation(float g) {
         return 0.5f * g * (1.0f + th);
     }
     return __fdividef(g, 1.0f + __expf(-g));
+}
+
+// act(gate) * up; with a limit (silu only) the clamped swish: g = min(gate, L), u = clamp(up, -L, L),
+// g * sigmoid(slope * g) * (u + 1)
+template <bool GELU>
+__device__ __forceinline__ float gated_pair(float g, float up, float limit, float slope) {
+    if (!GELU && limit > 0.f) {
+        g = fminf(g, limit);
+        up = fminf(fmaxf(up, -limit), limit) + 1.0f;
+        return __fdividef(g, 1.0f + __expf(-slope * g)) * up;
+    }
+    return gated_activation<GELU>(g) * up;
 }
 
 __device__ __forceinline__ void grid_dependents_may_launch() {
@@ -170,7 +184,7 @@ __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* t
                 // even lanes hold a gate row, the next lane the matching up row
                 const float up = __shfl_down_sync(0xffffffffu, val, 1);
                 const float g = val;
-                val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
+                val = gated_pair<MODE == OUT_BF16_GEGLU>(g, up, a.glu_limit, a.glu_slope);
             }
             if (a.tma_store) {
                 if (writer) {
@@ -423,7 +437,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     if (GLU) {
                         const float up = __shfl_down_sync(0xffffffffu, val, 1);
                         const float g = val;
-                        val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
+                        val = gated_pair<MODE == OUT_BF16_GEGLU>(g, up, a.glu_limit, a.glu_slope);
                     }
                     if (writer && out_f < out_n) {
                         if (MODE == OUT_BF16 || GLU)
@@ -481,7 +495,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         if (GLU) {
                             const float up = __shfl_down_sync(0xffffffffu, v, 1);
                             const float g = v;
-                            v = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
+                            v = gated_pair<MODE == OUT_BF16_GEGLU>(g, up, a.glu_limit, a.glu_slope);
                         }
                         val[u] = v;
                     }
@@ -975,11 +989,11 @@ using namespace zlm;
 // *norm_fused says whether it did (it does not when the launch it chooses has no cluster; nothing is written
 // then and the caller runs the norm kernel).  The product after it takes X = norm_hb and scale_ssq / scale_p /
 // scale_eps: every output row t is multiplied by 1 / sqrt(sum_p scale_ssq[t, p] / K + eps) before the bias.
-ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
-                                int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
-                                const void* norm_gain, int norm_gain_dtype, float norm_offset, void* norm_hb,
-                                long ld_hb, float* norm_ssq, int* norm_fused, const float* scale_ssq, int scale_p,
-                                float scale_eps, cudaStream_t stream) {
+static int gemm_tc_run(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
+                       int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
+                       const void* norm_gain, int norm_gain_dtype, float norm_offset, void* norm_hb,
+                       long ld_hb, float* norm_ssq, int* norm_fused, const float* scale_ssq, int scale_p,
+                       float scale_eps, float glu_limit, float glu_slope, cudaStream_t stream) {
     if (norm_fused) *norm_fused = 0;
     if (T <= 0 || N <= 0) return 0;
     if (scale_ssq != nullptr && (T > 64 || scale_p <= 0)) return ZLM_ERR_BAD_ARG;
@@ -999,6 +1013,8 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
     a.bias = bias; a.bias_dtype = bias_dtype; a.Y = Y; a.ldy = ldy; a.T = T; a.N = N; a.K = K;
     a.kb_total = (K + TC_BK - 1) / TC_BK;
     a.glu_kind = glu == 2 ? 1 : 0;
+    a.glu_limit = glu == 1 ? glu_limit : 0.f;
+    a.glu_slope = glu_slope;
     a.ksplit = 1;
     a.err = error_word();
     a.norm_gain = nullptr; a.norm_gain_dtype = norm_gain_dtype; a.norm_offset = norm_offset;
@@ -1074,11 +1090,83 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
     }
 }
 
+ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
+                                int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
+                                const void* norm_gain, int norm_gain_dtype, float norm_offset, void* norm_hb,
+                                long ld_hb, float* norm_ssq, int* norm_fused, const float* scale_ssq, int scale_p,
+                                float scale_eps, cudaStream_t stream) {
+    return gemm_tc_run(X, W, bias, bias_dtype, Y, y_dtype, accumulate, glu, T, N, K, ldx, ldw, ldy, splits, norm_gain,
+                       norm_gain_dtype, norm_offset, norm_hb, ld_hb, norm_ssq, norm_fused, scale_ssq, scale_p, scale_eps,
+                       0.f, 1.f, stream);
+}
+
+// The gated product with the clamped swish in its epilogue: the rows of W alternate gate and up rows, and
+// Y[t, j] = g sigmoid(slope g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), as bf16.
+ZLM_EXPORT int zlm_gemm_tc_swish_clamped(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int T,
+                                         int N, int K, long ldx, long ldw, long ldy, float limit, float slope,
+                                         cudaStream_t stream) {
+    if (!(limit > 0.f)) return ZLM_ERR_BAD_ARG;
+    return gemm_tc_run(X, W, bias, bias_dtype, Y, ZLM_BF16, 0, 1, T, N, K, ldx, ldw, ldy, 0, nullptr, ZLM_F32, 0.f, nullptr, 0,
+                       nullptr, nullptr, nullptr, 0, 0.f, limit, slope, stream);
+}
+
 ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
                            int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
                            cudaStream_t stream) {
     return zlm_gemm_tc_norm(X, W, bias, bias_dtype, Y, y_dtype, accumulate, glu, T, N, K, ldx, ldw, ldy, splits, nullptr,
                             ZLM_F32, 0.f, nullptr, 0, nullptr, nullptr, nullptr, 0, 0.f, stream);
+}
+
+// One product per group of consecutive rows, each group with a matrix of its own (the experts of a mixture):
+// rows host_offs[g] .. host_offs[g + 1] of X meet W + g * w_group_stride and give the same rows of Y.  The
+// offsets are host memory: the caller has read them back.  A group without rows launches nothing.  A group's
+// product is small (a few hundred rows) and fills a fraction of the GPU, so the groups are dealt out over a few
+// streams of this library that fork from `stream` and join it again; they write disjoint rows.
+constexpr int GROUP_STREAMS = 4;
+
+ZLM_EXPORT int zlm_gemm_tc_groups(const void* X, const void* W, void* Y, int y_dtype, int glu, const int* host_offs,
+                                  int n_groups, int N, int K, long ldx, long ldw, long ldy, long w_group_stride,
+                                  int* launched, cudaStream_t stream) {
+    static cudaStream_t side[GROUP_STREAMS];
+    static cudaEvent_t forked, joined[GROUP_STREAMS];
+    static bool made = false;
+    if (launched) *launched = 0;
+    if (n_groups <= 0 || !host_offs) return ZLM_ERR_BAD_ARG;
+    if (!made) {
+        if (cudaEventCreateWithFlags(&forked, cudaEventDisableTiming) != cudaSuccess) return (int)cudaGetLastError();
+        for (int i = 0; i < GROUP_STREAMS; ++i) {
+            if (cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&joined[i], cudaEventDisableTiming) != cudaSuccess)
+                return (int)cudaGetLastError();
+        }
+        made = true;
+    }
+    int busy = 0;
+    for (int g = 0; g < n_groups; ++g) busy += host_offs[g + 1] > host_offs[g] ? 1 : 0;
+    const int lanes = busy < GROUP_STREAMS ? 1 : GROUP_STREAMS;          // a group or two: the caller's stream will do
+    if (lanes > 1) {
+        cudaEventRecord(forked, stream);
+        for (int i = 0; i < lanes; ++i) cudaStreamWaitEvent(side[i], forked, 0);
+    }
+    const size_t y_el = y_dtype == ZLM_F32 ? 4 : 2;
+    int n = 0, rc = 0;
+    for (int g = 0; g < n_groups && rc == 0; ++g) {
+        const int rows = host_offs[g + 1] - host_offs[g];
+        if (rows <= 0) continue;
+        rc = zlm_gemm_tc((const __nv_bfloat16*)X + (long)host_offs[g] * ldx,
+                         (const __nv_bfloat16*)W + (long)g * w_group_stride, nullptr, ZLM_F32,
+                         (char*)Y + (size_t)host_offs[g] * ldy * y_el, y_dtype, 0, glu, rows, N, K, ldx, ldw, ldy, 0,
+                         lanes > 1 ? side[n % lanes] : stream);
+        ++n;
+    }
+    if (lanes > 1) {
+        for (int i = 0; i < lanes; ++i) {
+            cudaEventRecord(joined[i], side[i]);
+            cudaStreamWaitEvent(stream, joined[i], 0);
+        }
+    }
+    if (launched) *launched = rc == 0 ? n : n - 1;
+    return rc;
 }
 
 // Reads and clears the error word the kernels report bounded-wait failures through (synchronises the device).

@@ -21,18 +21,42 @@ namespace zlm {
 constexpr int GM = 32, GN = 64, GK = 32;
 
 // ------------------------------------------------------------------- routing
-// one warp per token; shared: choice[E], group score[n_groups]
-__global__ void route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int E, int top,
-                             int n_groups, int keep_groups, int group_best, int softmax_scores, int renormalize,
-                             int* __restrict__ ids, float* __restrict__ weights) {
+// one block of RT_WARPS warps per token; shared: score[E], choice[E], group score[n_groups], and the token's
+// row when the router's product is taken here.  z != null: the router logits were computed before.  Otherwise
+// z_e = sum_i h[t, i] * w[e, i] is taken here, a warp per expert with the lanes walking the row in a fixed
+// order (steps of few tokens: a product kernel of its own would cost more than the whole routing).
+constexpr int RT_WARPS = 4;
+
+template <typename TH>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_stride, const TH* __restrict__ w, int d,
+             const float* __restrict__ correction, int E, int top, int n_groups, int keep_groups, int group_best,
+             int softmax_scores, int renormalize, int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float sm[];
     float* score = sm;                 // [E]
     float* choice = sm + E;            // [E]
     float* gscore = sm + 2 * E;        // [n_groups]
+    float* logit = gscore + n_groups;  // [E]
+    float* row = logit + E;            // [d] when the product is taken here
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, lane = threadIdx.x;
-    const float* zr = z + (long)t * E;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (z != nullptr) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) logit[e] = z[(long)t * E + e];
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) row[i] = to_float(h[(long)t * h_stride + i]);
+        __syncthreads();
+        for (int e = warp; e < E; e += RT_WARPS) {
+            const TH* we = w + (long)e * d;
+            float acc = 0.f;
+            for (int i = lane; i < d; i += 32) acc = fmaf(row[i], to_float(we[i]), acc);
+            acc = warp_sum(acc);
+            if (lane == 0) logit[e] = acc;
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    const float* zr = logit;
     float zmax = -INFINITY, zsum = 0.f;
     if (softmax_scores) {
         for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, zr[e]);
@@ -105,7 +129,8 @@ __global__ void route_kernel(const float* __restrict__ z, const float* __restric
 // ------------------------------------------------------------------ grouping
 // one block.  counts -> offsets -> sorted pairs and tiles.
 __global__ void group_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ offs, int* __restrict__ sorted,
-                             int* __restrict__ tile_expert, int* __restrict__ tile_row, int* __restrict__ n_tiles) {
+                             int* __restrict__ place, int* __restrict__ tile_expert, int* __restrict__ tile_row,
+                             int* __restrict__ n_tiles) {
     extern __shared__ int smi[];
     int* count = smi;             // [E]
     int* start = smi + E;         // [E + 1]
@@ -131,22 +156,24 @@ __global__ void group_kernel(const int* __restrict__ ids, int P, int E, int* __r
     // pair p goes to the place its rank among its expert's pairs gives it: pairs in ascending order
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    if (P <= 4096) {
+    if (P <= 1024) {
         // few pairs: a stable order, so that a row's place does not depend on the timing of the threads
         if (threadIdx.x < E) {
             int at = start[threadIdx.x];
             for (int p = 0; p < P; ++p)
-                if (ids[p] == (int)threadIdx.x) sorted[at++] = p;
+                if (ids[p] == (int)threadIdx.x) { place[p] = at; sorted[at++] = p; }
         }
         for (int e = blockDim.x + threadIdx.x; e < E; e += blockDim.x) {
             int at = start[e];
             for (int p = 0; p < P; ++p)
-                if (ids[p] == e) sorted[at++] = p;
+                if (ids[p] == e) { place[p] = at; sorted[at++] = p; }
         }
     } else {
         for (int p = threadIdx.x; p < P; p += blockDim.x) {
             const int e = ids[p];
-            sorted[start[e] + atomicAdd(&count[e], 1)] = p;
+            const int at = start[e] + atomicAdd(&count[e], 1);
+            sorted[at] = p;
+            place[p] = at;
         }
     }
 }
@@ -158,7 +185,7 @@ __global__ void group_kernel(const int* __restrict__ ids, int P, int E, int* __r
 template <typename TX, typename TW, bool GLU>
 __global__ void __launch_bounds__(256)
 grouped_kernel(const TX* __restrict__ x, long x_stride, const TW* __restrict__ w, void* __restrict__ out_, long out_stride,
-               int N, int K, int top, const int* __restrict__ offs, const int* __restrict__ sorted,
+               int N, int K, int top, int interleaved, const int* __restrict__ offs, const int* __restrict__ sorted,
                const int* __restrict__ tile_expert, const int* __restrict__ tile_row, const int* __restrict__ n_tiles) {
     __shared__ float xs[GK][GM + 1];
     __shared__ float ws[GLU ? 2 : 1][GK][GN + 1];
@@ -189,8 +216,10 @@ grouped_kernel(const TX* __restrict__ x, long x_stride, const TW* __restrict__ w
             const int r = i / GK, k = i % GK;
             const int n = n0 + r;
             const bool ok = n < N && k0 + k < K;
-            ws[0][k][r] = ok ? to_float(we[(long)n * K + k0 + k]) : 0.f;
-            if (GLU) ws[1][k][r] = ok ? to_float(we[(long)(N + n) * K + k0 + k]) : 0.f;
+            // gate row n and up row n: rows (n, N + n), or (2n, 2n + 1) when the two alternate
+            const long g_row = (GLU && interleaved) ? 2L * n : n, u_row = (GLU && interleaved) ? 2L * n + 1 : (long)N + n;
+            ws[0][k][r] = ok ? to_float(we[g_row * K + k0 + k]) : 0.f;
+            if (GLU) ws[1][k][r] = ok ? to_float(we[u_row * K + k0 + k]) : 0.f;
         }
         __syncthreads();
         const int kmax = min(GK, K - k0);
@@ -225,9 +254,117 @@ grouped_kernel(const TX* __restrict__ x, long x_stride, const TW* __restrict__ w
     }
 }
 
-// out[t, :] (+)= sum_k weights[t, k] * y[t * top + k, :]
-__global__ void combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, float* __restrict__ out,
-                               long total, int d, int top, int accumulate) {
+// The same products for steps of few tokens, where an expert has a handful of rows and the time is the time to
+// read its weights once: a warp takes a weight row (gate and up rows together), its lanes walk K sixteen bytes at
+// a time, and the row meets up to SK_ROWS input rows held in shared memory; a warp-wide sum ends each output.
+constexpr int SK_ROWS = 8, SK_WARPS = 8, SK_PER_WARP = 4;      // a block: 32 weight rows (or pairs of them)
+
+template <typename TW> struct Vec16;
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename TW> __device__ __forceinline__ void load16(const TW* p, float (&f)[Vec16<TW>::N]);
+template <> __device__ __forceinline__ void load16<float>(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(h[i]);
+        f[2 * i] = v.x; f[2 * i + 1] = v.y;
+    }
+}
+
+template <typename TX, bool GLU>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+grouped_skinny_kernel(const TX* __restrict__ x, long x_stride, const TX* __restrict__ w, void* __restrict__ out_,
+                      long out_stride, int N, int K, int top, int interleaved, const int* __restrict__ offs,
+                      const int* __restrict__ sorted, const int* __restrict__ tile_expert,
+                      const int* __restrict__ tile_row, const int* __restrict__ n_tiles) {
+    extern __shared__ __align__(16) unsigned char sk_raw[];
+    TX* xs = reinterpret_cast<TX*>(sk_raw);                     // [SK_ROWS][K]
+    __shared__ int row_in[SK_ROWS], row_out[SK_ROWS];
+    constexpr int V = Vec16<TX>::N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.y;
+    if (tile >= n_tiles[0]) return;
+    const int e = tile_expert[tile], r_first = tile_row[tile];
+    const int rows_all = min(GM, offs[e + 1] - r_first);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TX* we = w + (long)e * (GLU ? 2 : 1) * N * K;
+    for (int r0 = 0; r0 < rows_all; r0 += SK_ROWS) {
+        const int rows = min(SK_ROWS, rows_all - r0);
+        __syncthreads();                                        // the rows before are done with
+        if (threadIdx.x < SK_ROWS) {
+            const int s = r_first + r0 + threadIdx.x;
+            const int pair = (int)threadIdx.x < rows ? sorted[s] : 0;
+            row_in[threadIdx.x] = GLU ? pair / top : s;
+            row_out[threadIdx.x] = GLU ? s : pair;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < SK_ROWS * (K / V); i += blockDim.x) {
+            const int r = i / (K / V), k = (i % (K / V)) * V;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < rows) v = *reinterpret_cast<const uint4*>(x + (long)row_in[r] * x_stride + k);
+            *reinterpret_cast<uint4*>(xs + (long)r * K + k) = v;
+        }
+        __syncthreads();
+        for (int j = 0; j < SK_PER_WARP; ++j) {
+            const int n = (blockIdx.x * SK_WARPS + warp) * SK_PER_WARP + j;
+            if (n >= N) break;
+            const long g_row = (GLU && interleaved) ? 2L * n : n, u_row = (GLU && interleaved) ? 2L * n + 1 : (long)N + n;
+            float acc[GLU ? 2 : 1][SK_ROWS] = {};
+            for (int k = lane * V; k < K; k += 32 * V) {
+                float wg[V], wu[V];
+                load16<TX>(we + g_row * K + k, wg);
+                if (GLU) load16<TX>(we + u_row * K + k, wu);
+#pragma unroll
+                for (int r = 0; r < SK_ROWS; ++r) {
+                    float xv[V];
+                    load16<TX>(xs + (long)r * K + k, xv);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        acc[0][r] = fmaf(xv[i], wg[i], acc[0][r]);
+                        if (GLU) acc[GLU ? 1 : 0][r] = fmaf(xv[i], wu[i], acc[GLU ? 1 : 0][r]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < SK_ROWS; ++r) {
+                const float g = warp_sum(acc[0][r]);
+                const float u = GLU ? warp_sum(acc[GLU ? 1 : 0][r]) : 0.f;
+                if (lane == 0 && r < rows) {
+                    if (GLU) {
+                        const float gr = round_to<TX>(g), ur = round_to<TX>(u);
+                        ((TX*)out_)[(long)row_out[r] * out_stride + n] = from_float<TX>((gr / (1.0f + expf(-gr))) * ur);
+                    } else {
+                        ((float*)out_)[(long)row_out[r] * out_stride + n] = g;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// rows[s, :] = x[sorted[s] / top, :]: the tokens' rows in grouped order, for products that want contiguous rows
+template <typename T>
+__global__ void gather_kernel(const T* __restrict__ x, long x_stride, const int* __restrict__ sorted, int top,
+                              T* __restrict__ rows, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long s = blockIdx.x;
+    const T* src = x + (long)(sorted[s] / top) * x_stride;
+    T* dst = rows + s * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+}
+
+// out[t, :] (+)= sum_k weights[t, k] * y[row(t * top + k), :], row(p) = p, or place[p] when y is in grouped order
+__global__ void combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ place,
+                               float* __restrict__ out, long total, int d, int top, int accumulate) {
     pdl_launch_dependents();
     pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -235,7 +372,10 @@ __global__ void combine_kernel(const float* __restrict__ y, const float* __restr
     const long t = idx / d;
     const int i = (int)(idx % d);
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(weights[t * top + k], y[(t * top + k) * d + i], acc);
+    for (int k = 0; k < top; ++k) {
+        const long p = t * top + k;
+        acc = fmaf(weights[p], y[(place ? (long)place[p] : p) * d + i], acc);
+    }
     out[idx] = accumulate ? out[idx] + acc : acc;
 }
 
@@ -243,49 +383,86 @@ __global__ void combine_kernel(const float* __restrict__ y, const float* __restr
 
 using namespace zlm;
 
-ZLM_EXPORT int zlm_moe_route(const float* z, const float* correction, int T, int E, int top, int n_groups,
-                             int keep_groups, int group_best, int softmax_scores, int renormalize, int* ids,
-                             float* weights, cudaStream_t stream) {
+// z: float [T, E] router logits, or null: then h [T, d] (rows with a stride) and w [E, d] of one storage type are
+// given and the logits are taken here.
+ZLM_EXPORT int zlm_moe_route(const float* z, const void* h, int h_dtype, long h_stride, const void* w, int d,
+                             const float* correction, int T, int E, int top, int n_groups, int keep_groups,
+                             int group_best, int softmax_scores, int renormalize, int* ids, float* weights,
+                             cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || n_groups <= 0 || E % n_groups || keep_groups <= 0 || keep_groups > n_groups ||
-        group_best <= 0 || top > keep_groups * (E / n_groups))
+        group_best <= 0 || top > keep_groups * (E / n_groups) || (!z && (!h || !w || d <= 0)))
         return ZLM_ERR_BAD_ARG;
-    const size_t smem = (2 * (size_t)E + n_groups) * sizeof(float);
+    const size_t smem = (3 * (size_t)E + n_groups + (z ? 0 : d)) * sizeof(float);
     if (smem > 48 * 1024) return ZLM_ERR_UNSUPPORTED;
-    cudaError_t e = launch_pdl(route_kernel, dim3(T), dim3(32), smem, stream, z, correction, E, top, n_groups,
-                               keep_groups, group_best, softmax_scores, renormalize, ids, weights);
+    cudaError_t e;
+    if (z || h_dtype == ZLM_F32)
+        e = launch_pdl(route_kernel<float>, dim3(T), dim3(RT_WARPS * 32), smem, stream, z, (const float*)h, h_stride,
+                       (const float*)w, d, correction, E, top, n_groups, keep_groups, group_best, softmax_scores,
+                       renormalize, ids, weights);
+    else if (h_dtype == ZLM_BF16)
+        e = launch_pdl(route_kernel<__nv_bfloat16>, dim3(T), dim3(RT_WARPS * 32), smem, stream, z, (const __nv_bfloat16*)h,
+                       h_stride, (const __nv_bfloat16*)w, d, correction, E, top, n_groups, keep_groups, group_best,
+                       softmax_scores, renormalize, ids, weights);
+    else
+        return ZLM_ERR_UNSUPPORTED;
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 // The most tiles P pairs over E experts can make.
 ZLM_EXPORT long zlm_moe_max_tiles_scratch(int P, int E) { return (long)(P + GM - 1) / GM + E; }
 
-ZLM_EXPORT int zlm_moe_group(const int* ids, int P, int E, int* offs, int* sorted, int* tile_expert, int* tile_row,
-                             int* n_tiles, cudaStream_t stream) {
+// place[p]: where pair p stands in ``sorted`` (the inverse of it).
+ZLM_EXPORT int zlm_moe_group(const int* ids, int P, int E, int* offs, int* sorted, int* place, int* tile_expert,
+                             int* tile_row, int* n_tiles, cudaStream_t stream) {
     if (P <= 0) return 0;
     if (E <= 0) return ZLM_ERR_BAD_ARG;
     const size_t smem = (2 * (size_t)E + 1) * sizeof(int);
     if (smem > 48 * 1024) return ZLM_ERR_UNSUPPORTED;
-    cudaError_t e = launch_pdl(group_kernel, dim3(1), dim3(1024), smem, stream, ids, P, E, offs, sorted, tile_expert,
-                               tile_row, n_tiles);
+    cudaError_t e = launch_pdl(group_kernel, dim3(1), dim3(1024), smem, stream, ids, P, E, offs, sorted, place,
+                               tile_expert, tile_row, n_tiles);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 // glu != 0: x [T, K] (rows by token) -> out [P, N] storage type, sorted order, w [E, 2N, K]
 // glu == 0: x [P, K] (sorted order)  -> out [P, N] float, pair order, w [E, N, K]
+// interleaved (glu only): gate row n and up row n of an expert are rows 2n and 2n + 1 of its matrix.
+// skinny: the step has few tokens; an expert's weights are streamed once against up to 8 rows at a time.
 ZLM_EXPORT int zlm_moe_grouped(const void* x, int x_dtype, long x_stride, const void* w, int w_dtype, void* out,
-                               long out_stride, int glu, int P, int E, int N, int K, int top, const int* offs,
-                               const int* sorted, const int* tile_expert, const int* tile_row, const int* n_tiles,
-                               cudaStream_t stream) {
+                               long out_stride, int glu, int interleaved, int skinny, int P, int E, int N, int K, int top,
+                               const int* offs, const int* sorted, const int* tile_expert, const int* tile_row,
+                               const int* n_tiles, cudaStream_t stream) {
     if (P <= 0) return 0;
     if (E <= 0 || N <= 0 || K <= 0 || top <= 0) return ZLM_ERR_BAD_ARG;
     const long max_tiles = zlm_moe_max_tiles_scratch(P, E);
     if (max_tiles > 65535) return ZLM_ERR_UNSUPPORTED;
-    dim3 grid((N + GN - 1) / GN, (unsigned)max_tiles);
     cudaError_t e;
+    const int el = x_dtype == ZLM_F32 ? 4 : 2;
+    const size_t sk_smem = (size_t)SK_ROWS * K * el;
+    if (skinny && x_dtype == w_dtype && K % (16 / el) == 0 && x_stride % (16 / el) == 0 && (uintptr_t)x % 16 == 0 &&
+        (uintptr_t)w % 16 == 0 && sk_smem <= 160 * 1024) {
+        dim3 sgrid((N + SK_WARPS * SK_PER_WARP - 1) / (SK_WARPS * SK_PER_WARP), (unsigned)max_tiles);
+#define ZLM_SK(TX, GLU)                                                                                              \
+    do {                                                                                                             \
+        static size_t allowed = 0;                                                                                   \
+        if (sk_smem > 48 * 1024 && sk_smem > allowed) {                                                              \
+            cudaError_t ea = cudaFuncSetAttribute(grouped_skinny_kernel<TX, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                  160 * 1024);                                                       \
+            if (ea != cudaSuccess) return (int)ea;                                                                   \
+            allowed = 160 * 1024;                                                                                    \
+        }                                                                                                            \
+        e = launch_pdl(grouped_skinny_kernel<TX, GLU>, sgrid, dim3(SK_WARPS * 32), sk_smem, stream, (const TX*)x, x_stride, \
+                       (const TX*)w, out, out_stride, N, K, top, interleaved, offs, sorted, tile_expert, tile_row, n_tiles); \
+    } while (0)
+        if (x_dtype == ZLM_F32) { if (glu) ZLM_SK(float, true); else ZLM_SK(float, false); }
+        else { if (glu) ZLM_SK(__nv_bfloat16, true); else ZLM_SK(__nv_bfloat16, false); }
+#undef ZLM_SK
+        return e == cudaSuccess ? launch_status() : (int)e;
+    }
+    dim3 grid((N + GN - 1) / GN, (unsigned)max_tiles);
 #define ZLM_GR(TX, TW, GLU)                                                                                         \
     e = launch_pdl(grouped_kernel<TX, TW, GLU>, grid, dim3(256), 0, stream, (const TX*)x, x_stride, (const TW*)w, out, \
-                   out_stride, N, K, top, offs, sorted, tile_expert, tile_row, n_tiles)
+                   out_stride, N, K, top, interleaved, offs, sorted, tile_expert, tile_row, n_tiles)
     if (x_dtype == ZLM_F32 && w_dtype == ZLM_F32) { if (glu) ZLM_GR(float, float, true); else ZLM_GR(float, float, false); }
     else if (x_dtype == ZLM_BF16 && w_dtype == ZLM_BF16) { if (glu) ZLM_GR(__nv_bfloat16, __nv_bfloat16, true); else ZLM_GR(__nv_bfloat16, __nv_bfloat16, false); }
     else return ZLM_ERR_UNSUPPORTED;
@@ -293,12 +470,28 @@ ZLM_EXPORT int zlm_moe_grouped(const void* x, int x_dtype, long x_stride, const 
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
-ZLM_EXPORT int zlm_moe_combine(const float* y, const float* weights, float* out, int T, int d, int top, int accumulate,
-                               cudaStream_t stream) {
+ZLM_EXPORT int zlm_moe_gather(const void* x, int dtype, long x_stride, const int* sorted, int top, void* rows, int P,
+                              int d, cudaStream_t stream) {
+    if (P <= 0) return 0;
+    if (d <= 0 || top <= 0) return ZLM_ERR_BAD_ARG;
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(gather_kernel<float>, dim3(P), dim3(256), 0, stream, (const float*)x, x_stride, sorted, top, (float*)rows, d);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(gather_kernel<__nv_bfloat16>, dim3(P), dim3(256), 0, stream, (const __nv_bfloat16*)x, x_stride, sorted,
+                       top, (__nv_bfloat16*)rows, d);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// place: null when row p of y is pair p; else y is in grouped order and place[p] is pair p's row.
+ZLM_EXPORT int zlm_moe_combine(const float* y, const float* weights, const int* place, float* out, int T, int d, int top,
+                               int accumulate, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || top <= 0) return ZLM_ERR_BAD_ARG;
     const long total = (long)T * d;
-    cudaError_t e = launch_pdl(combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights, out,
-                               total, d, top, accumulate);
+    cudaError_t e = launch_pdl(combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights, place,
+                               out, total, d, top, accumulate);
     return e == cudaSuccess ? launch_status() : (int)e;
 }

@@ -72,13 +72,14 @@ _PROTOTYPES = {
                            c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "moe": {
-        "zlm_moe_route": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                          c_void_p],
+        "zlm_moe_route": [c_void_p, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "zlm_moe_max_tiles_scratch": [c_int, c_int],
-        "zlm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "zlm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "zlm_moe_grouped": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
-                            c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
-        "zlm_moe_combine": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "zlm_moe_gather": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+        "zlm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_generic": {
         "zlm_gemm_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -119,6 +120,10 @@ _PROTOTYPES = {
         "zlm_gemm_tc_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_long, c_long, c_long, c_int, c_void_p, c_int, c_float, c_void_p, c_long, c_void_p,
                              c_void_p, c_void_p, c_int, c_float, c_void_p],
+        "zlm_gemm_tc_swish_clamped": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_long, c_long,
+                                      c_long, c_float, c_float, c_void_p],
+        "zlm_gemm_tc_groups": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_long, c_long,
+                               c_long, c_long, c_void_p, c_void_p],
         "zlm_gemm_tc_status": [c_void_p],
         "zlm_gemm_tc_wait_selftest": [c_int, c_void_p, c_void_p],
     },
@@ -352,51 +357,68 @@ def gated_scan(u: torch.Tensor, gates: torch.Tensor, gate_block: int, y: torch.T
 
 
 # ------------------------------------------------------------ mixture of experts
-def moe_route(z: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int, keep_groups: int,
+def moe_route(z: Optional[torch.Tensor], correction: Optional[torch.Tensor], top: int, n_groups: int, keep_groups: int,
               group_best: int, ids: torch.Tensor, weights: torch.Tensor, softmax_scores: bool = False,
-              renormalize: bool = False) -> None:
+              renormalize: bool = False, h: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None) -> None:
     """Per token: scores = sigmoid(z) (or softmax), chosen by score + correction within the ``keep_groups`` groups
     whose ``group_best`` best choice scores sum highest; ids int32 [T, top], weights float32 [T, top] (the scores
-    of the chosen, divided by their sum with ``renormalize``)."""
-    _cuda(z, "z", torch.float32); _cuda(ids, "ids", torch.int32); _cuda(weights, "weights", torch.float32)
-    T, E = z.shape
+    of the chosen, divided by their sum with ``renormalize``).  ``z``: float32 [T, E] router logits; or None with
+    ``h`` [T, d] and ``router`` [E, d] of one type: the logits are then taken inside (float32 sums), which is what
+    a step of few tokens wants."""
+    _cuda(ids, "ids", torch.int32); _cuda(weights, "weights", torch.float32)
+    d, h_stride, h_code = 0, 0, F32
+    if z is not None:
+        _cuda(z, "z", torch.float32)
+        T, E = z.shape
+    else:
+        if h is None or router is None:
+            raise KernelError("moe_route: the logits, or the rows and the router's matrix, are needed")
+        _rows(h, "h"); _cuda(router, "router", h.dtype)
+        T, d = h.shape
+        E = router.shape[0]
+        if router.shape != (E, d):
+            raise KernelError("moe_route: the router's matrix must be [E, d]")
+        h_stride, h_code = _row_stride(h), code(h.dtype)
     if correction is not None:
         _cuda(correction, "correction", torch.float32)
         if correction.numel() != E:
             raise KernelError("moe_route: one correction per expert is needed")
     if ids.shape != (T, top) or weights.shape != (T, top):
         raise KernelError("moe_route: ids and weights must be [T, top]")
-    _check(_fn("moe", "zlm_moe_route")(z.data_ptr(), _ptr(correction), T, E, top, n_groups, keep_groups, group_best,
-                                       int(softmax_scores), int(renormalize), ids.data_ptr(), weights.data_ptr(),
-                                       _stream()), "moe_route")
+    _check(_fn("moe", "zlm_moe_route")(_ptr(z), _ptr(h), h_code, h_stride, _ptr(router), d, _ptr(correction), T, E, top,
+                                       n_groups, keep_groups, group_best, int(softmax_scores), int(renormalize),
+                                       ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
 
 
 def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
     return int(_fn("moe", "zlm_moe_max_tiles_scratch")(n_pairs, n_experts))
 
 
-def moe_group(ids: torch.Tensor, n_experts: int, offs: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor,
-              tile_row: torch.Tensor, n_tiles: torch.Tensor) -> None:
-    """Group the (token, choice) pairs by expert: ``order`` lists the pairs expert by expert, ``offs`` [E + 1] where
-    each expert's run starts, and the runs are cut into tiles of rows for the grouped products."""
-    for t, n in ((ids, "ids"), (offs, "offs"), (order, "order"), (tile_expert, "tile_expert"), (tile_row, "tile_row"),
-                 (n_tiles, "n_tiles")):
+def moe_group(ids: torch.Tensor, n_experts: int, offs: torch.Tensor, order: torch.Tensor, place: torch.Tensor,
+              tile_expert: torch.Tensor, tile_row: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """Group the (token, choice) pairs by expert: ``order`` lists the pairs expert by expert, ``place`` is its
+    inverse (where pair p stands in ``order``), ``offs`` [E + 1] says where each expert's run starts, and the runs
+    are cut into tiles of rows for the grouped products."""
+    for t, n in ((ids, "ids"), (offs, "offs"), (order, "order"), (place, "place"), (tile_expert, "tile_expert"),
+                 (tile_row, "tile_row"), (n_tiles, "n_tiles")):
         _cuda(t, n, torch.int32)
     P = ids.numel()
     need = moe_max_tiles(P, n_experts)
-    if offs.numel() < n_experts + 1 or order.numel() < P or tile_expert.numel() < need or tile_row.numel() < need:
+    if (offs.numel() < n_experts + 1 or order.numel() < P or place.numel() < P or tile_expert.numel() < need
+            or tile_row.numel() < need):
         raise KernelError("moe_group: an output is too short")
-    _check(_fn("moe", "zlm_moe_group")(ids.data_ptr(), P, n_experts, offs.data_ptr(), order.data_ptr(),
+    _check(_fn("moe", "zlm_moe_group")(ids.data_ptr(), P, n_experts, offs.data_ptr(), order.data_ptr(), place.data_ptr(),
                                        tile_expert.data_ptr(), tile_row.data_ptr(), n_tiles.data_ptr(), _stream()),
            "moe_group")
 
 
 def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, glu: bool, n_pairs: int, top: int,
                 offs: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor, tile_row: torch.Tensor,
-                n_tiles: torch.Tensor) -> None:
+                n_tiles: torch.Tensor, interleaved: bool = False, skinny: bool = False) -> None:
     """The experts' products over the grouped pairs.  ``glu``: x [T, K] by token, w [E, 2N, K] (gate rows, then up
-    rows), out [P, N] = silu(gate) * up in x's type, rows in grouped order.  Otherwise: x [P, K] in grouped order,
-    w [E, N, K], out float32 [P, N] with row p the result of pair p."""
+    rows; alternating with ``interleaved``), out [P, N] = silu(gate) * up in x's type, rows in grouped order.
+    Otherwise: x [P, K] in grouped order, w [E, N, K], out float32 [P, N] with row p the result of pair p.
+    ``skinny``: the step has few tokens, so an expert's weights are streamed once against its few rows."""
     _rows(x, "x"); _cuda(w, "w"); _rows(out, "out")
     E, NW, K = w.shape
     N = NW // 2 if glu else NW
@@ -404,19 +426,58 @@ def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, glu: bool, 
         raise KernelError("moe_grouped: shapes or types do not match")
     _check(_fn("moe", "zlm_moe_grouped")(
         x.data_ptr(), code(x.dtype), _row_stride(x), w.data_ptr(), code(w.dtype), out.data_ptr(), _row_stride(out),
-        int(glu), n_pairs, E, N, K, top, offs.data_ptr(), order.data_ptr(), tile_expert.data_ptr(), tile_row.data_ptr(),
-        n_tiles.data_ptr(), _stream()), "moe_grouped")
+        int(glu), int(interleaved), int(skinny), n_pairs, E, N, K, top, offs.data_ptr(), order.data_ptr(),
+        tile_expert.data_ptr(), tile_row.data_ptr(), n_tiles.data_ptr(), _stream()), "moe_grouped")
 
 
-def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, accumulate: bool) -> None:
-    """out[t] (+)= sum_k weights[t, k] * y[t * top + k], k ascending; all float32."""
+def moe_gather(x: torch.Tensor, order: torch.Tensor, top: int, rows: torch.Tensor) -> None:
+    """rows[s] = x[order[s] // top]: the tokens' rows in grouped order."""
+    _rows(x, "x"); _cuda(rows, "rows", x.dtype); _cuda(order, "order", torch.int32)
+    P, d = rows.shape
+    if x.shape[1] != d or order.numel() < P:
+        raise KernelError("moe_gather: shapes do not match")
+    _check(_fn("moe", "zlm_moe_gather")(x.data_ptr(), code(x.dtype), _row_stride(x), order.data_ptr(), top,
+                                        rows.data_ptr(), P, d, _stream()), "moe_gather")
+
+
+def gemm_tc_groups(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, host_offs, glu: Optional[str] = None) -> bool:
+    """One tensor-core product per group of consecutive rows: rows host_offs[g]..host_offs[g+1] of x [P, K] meet
+    w[g] ([G, N, K], bf16) and give the same rows of out ([P, N], or [P, N/2] bf16 with ``glu``, whose rows of
+    w[g] alternate gate and up).  ``host_offs``: a C array of G + 1 ints on the host.  False, with nothing or only
+    some groups done, if the operands are not what TMA can read."""
+    global _launches
+    _cuda(x, "x", torch.bfloat16); _cuda(w, "w", torch.bfloat16); _cuda(out, "out")
+    G, N, K = w.shape
+    n_out = N // 2 if glu else N
+    if x.shape[1] != K or out.shape != (x.shape[0], n_out) or (glu and out.dtype != torch.bfloat16):
+        raise KernelError("gemm_tc_groups: shapes or types do not match")
+    launched = ctypes.c_int(0)
+    status = _fn("gemm_tc", "zlm_gemm_tc_groups")(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), code(out.dtype), GLU_KINDS[glu] if glu else 0, host_offs, G, N, K,
+        K, K, n_out, N * K, ctypes.byref(launched), _stream())
+    _launches += launched.value
+    if status == -2:
+        return False
+    if status != 0:
+        _check(status, "gemm_tc_groups")
+    return True
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, accumulate: bool,
+                place: Optional[torch.Tensor] = None) -> None:
+    """out[t] (+)= sum_k weights[t, k] * y[row(t * top + k)], k ascending; all float32.  row(p) = p, or
+    ``place[p]`` when y is in grouped order."""
     _cuda(y, "y", torch.float32); _cuda(weights, "weights", torch.float32); _cuda(out, "out", torch.float32)
     T, top = weights.shape
     d = out.shape[1]
     if y.shape != (T * top, d) or out.shape[0] != T:
         raise KernelError("moe_combine: shapes do not match")
-    _check(_fn("moe", "zlm_moe_combine")(y.data_ptr(), weights.data_ptr(), out.data_ptr(), T, d, top, int(accumulate),
-                                         _stream()), "moe_combine")
+    if place is not None:
+        _cuda(place, "place", torch.int32)
+        if place.numel() < T * top:
+            raise KernelError("moe_combine: one place per pair is needed")
+    _check(_fn("moe", "zlm_moe_combine")(y.data_ptr(), weights.data_ptr(), _ptr(place), out.data_ptr(), T, d, top,
+                                         int(accumulate), _stream()), "moe_combine")
 
 
 def add_(y: torch.Tensor, x: torch.Tensor) -> None:
@@ -870,6 +931,32 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
         return False
     _check(status, "gemm_tc")
     return 2 if fused.value else 1
+
+
+def gemm_tc_swish_clamped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, limit: float, slope: float,
+                          bias: Optional[torch.Tensor] = None) -> bool:
+    """The gated product on the tensor cores with the clamped swish in its epilogue: the rows of w [2I, K] alternate
+    gate and up rows, out [T, I] (bf16) = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit) and
+    u = clamp(up, -limit, limit).  False, having done nothing, if the operands are not what TMA can read."""
+    for t, n in ((x, "x"), (w, "w"), (out, "out")):
+        _rows(t, n)
+        if t.dtype != torch.bfloat16:
+            raise KernelError(f"gemm_tc_swish_clamped: {n} must be bfloat16")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or N % 2 or out.shape != (T, N // 2) or not limit > 0:
+        raise KernelError("gemm_tc_swish_clamped: shapes do not match, or the limit is not positive")
+    if bias is not None:
+        _cuda(bias, "bias")
+        if bias.numel() != N:
+            raise KernelError("gemm_tc_swish_clamped: bias length does not match")
+    status = _fn("gemm_tc", "zlm_gemm_tc_swish_clamped")(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), code(bias.dtype) if bias is not None else F32, out.data_ptr(), T, N, K,
+        _row_stride(x), _row_stride(w), _row_stride(out), float(limit), float(slope), _stream())
+    if status == -2:
+        return False
+    _check(status, "gemm_tc_swish_clamped")
+    return True
 
 
 def gemm_tc_status() -> int:

@@ -40,9 +40,11 @@ class LatentAttention(Part):
         self.scale = float(spec.scale)
         if o.get("gate", "sigmoid") != "sigmoid":
             raise ValueError(f"latent_attention: output gate {o.get('gate')!r} is not known (sigmoid)")
-        if self.kv_rank % 8 or self.kv_rank > 512:
-            raise ValueError(f"latent_attention: a key/value latent of {self.kv_rank} elements is not supported "
-                             "(a multiple of 8, at most 512)")
+        # the attention kernels take head sizes that are multiples of 8: a latent of another size is kept with
+        # zeros behind it (they add nothing to a score and their part of the result is not read)
+        self.kept = -(-self.kv_rank // 8) * 8
+        if self.kept > 512:
+            raise ValueError(f"latent_attention: a key/value latent of {self.kv_rank} elements is not supported (at most 512)")
         eps = float(o["norm_eps"])
         norm_kind = o.get("norm", "rmsnorm")
         self.q_norm = norm_class(norm_kind)(NormSpec(norm_kind, self.q_rank, eps), dtype, device)
@@ -72,33 +74,41 @@ class LatentAttention(Part):
         self.o = Linear(tensors["o.weight"])
         self.q_norm.bind({"weight": tensors["dq_norm.weight"]})
         self.kv_norm.bind({"weight": tensors["dkv_norm.weight"]})
-        self.uk_t = tensors["uk.weight"].view(H, D, R).transpose(1, 2).contiguous()
-        self.uv = tensors["uv.weight"].view(H, V, R).contiguous()
+        uk_t = tensors["uk.weight"].view(H, D, R).transpose(1, 2)
+        uv = tensors["uv.weight"].view(H, V, R)
+        if self.kept != R:
+            pad = self.kept - R
+            uk_t = torch.cat([uk_t, uk_t.new_zeros(H, pad, D)], dim=1)
+            uv = torch.cat([uv, uv.new_zeros(H, V, pad)], dim=2)
+        self.uk_t = uk_t.contiguous()
+        self.uv = uv.contiguous()
 
     def kernel_libraries(self) -> Tuple[str, ...]:
         libs = ("elementwise", "block_linear", "attention")
-        libs += kernels.fast_attention_libraries(self.dtype, self.kv_rank, self.n_heads, 1)
+        libs += kernels.fast_attention_libraries(self.dtype, self.kept, self.n_heads, 1)
         for lin in (self.down, self.uq, self.o):
             if lin is not None:
                 libs += lin.libraries(self.dtype)
         return libs
 
     def cache_needs(self) -> Optional[KVNeed]:
-        return KVNeed(1, self.kv_rank, None, values_are_keys=True)
+        return KVNeed(1, self.kept, None, values_are_keys=True)
 
     def state_needs(self) -> Optional[StateNeed]:
         return None
 
     def forward(self, step, io: LayerIO, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True):
         T = residual.shape[0]
-        H, D, V, Rq, R = self.n_heads, self.dim, self.value_dim, self.q_rank, self.kv_rank
-        proj = step.ws.buf("lat_proj", (T, Rq + R + H * V), torch.float32)
+        H, D, V, Rq, Rn, R = self.n_heads, self.dim, self.value_dim, self.q_rank, self.kv_rank, self.kept
+        proj = step.ws.buf("lat_proj", (T, Rq + Rn + H * V), torch.float32)
         self.down(h, proj)
         cq = step.ws.buf("lat_cq", (T, Rq), self.dtype)
         self.q_norm.forward_rows(proj[:, :Rq], cq)
         # a row of ``qc``: the H queries in the latent's space, then the token's latent (the one key/value head)
         qc = step.ws.buf("lat_qc", (T, (H + 1) * R), self.dtype)
-        self.kv_norm.forward_rows(proj[:, Rq:Rq + R], qc[:, H * R:])
+        self.kv_norm.forward_rows(proj[:, Rq:Rq + Rn], qc[:, H * R:H * R + Rn])
+        if R != Rn:
+            qc[:, H * R + Rn:].zero_()
         q = step.ws.buf("lat_q", (T, H * D), self.dtype)
         self.uq(cq, q)
         kernels.block_linear(q, self.uk_t, qc[:, :H * R])
@@ -107,7 +117,7 @@ class LatentAttention(Part):
         mixed = step.ws.buf("lat_mixed", (T, H * R), self.dtype)
         kernels.attention(step, qc, mixed, H, 1, R, self.scale, None, io)
         heads = step.ws.buf("lat_heads", (T, H * V), self.dtype)
-        kernels.block_linear(mixed, self.uv, heads, epilogue="sigmoid_gate", gate=proj[:, Rq + R:])
+        kernels.block_linear(mixed, self.uv, heads, epilogue="sigmoid_gate", gate=proj[:, Rq + Rn:])
         self.o(heads, residual, accumulate=accumulate)
         return None
 

@@ -83,9 +83,13 @@ class GatedMLP(Part):
         act = step.ws.buf("ffn_act", (T, self.intermediate), self.dtype)
         normed = isinstance(h, NormedInput)
         rows = h.hb if normed else h
-        fused = (self.interleaved and self.spec.activation in kernels.GLU_KINDS
-                 and kernels.gemm_tc(rows, self.gate_up.weight, act, bias=self.gate_up.bias, glu=self.spec.activation,
-                                     row_scale=(h.ssq, h.eps) if normed else None))
+        if self.interleaved and self.spec.activation == "swish_clamped" and not normed:
+            fused = kernels.gemm_tc_swish_clamped(rows, self.gate_up.weight, act, self.limit, self.slope,
+                                                  bias=self.gate_up.bias)
+        else:
+            fused = (self.interleaved and self.spec.activation in kernels.GLU_KINDS
+                     and kernels.gemm_tc(rows, self.gate_up.weight, act, bias=self.gate_up.bias, glu=self.spec.activation,
+                                         row_scale=(h.ssq, h.eps) if normed else None))
         if not fused:
             gu = step.ws.buf("gate_up", (T, 2 * self.intermediate), self.dtype)
             self.gate_up(h, gu)

@@ -44,10 +44,12 @@ class MixtureOfExperts(Part):
             raise ValueError(f"moe: {E} experts in {G} groups of which {self.keep_groups} are kept cannot give "
                              f"{self.top} experts a token")
         self.ff = spec.intermediate
-        self.router: Optional[torch.Tensor] = None
+        self.router: Optional[Linear] = None
         self.correction: Optional[torch.Tensor] = None
         self.gate_up: Optional[torch.Tensor] = None     # [E, 2 ff, d]
         self.down: Optional[torch.Tensor] = None        # [E, d, ff]
+        self.interleaved = False                        # gate and up rows of an expert alternate (bfloat16)
+        self._host_offs = None                          # the experts' offsets read back for a prompt step
 
     @classmethod
     def declare(cls, spec: FeedForwardSpec) -> Dict[str, ParamDecl]:
@@ -64,42 +66,81 @@ class MixtureOfExperts(Part):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         E = self.n_experts
-        self.router = tensors["router.weight"].contiguous()
+        self.router = Linear(tensors["router.weight"])
         self.correction = tensors["correction"].float().contiguous() if "correction" in tensors else None
         mats = [tensors[f"e{e}.{n}.weight"] for e in range(E) for n in ("gate", "up", "down")]
         wide = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
-        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate.weight"].to(wide), tensors[f"e{e}.up.weight"].to(wide)], dim=0)
+        # bfloat16: gate and up rows alternate, which is what the tensor-core product's gated epilogue reads
+        self.interleaved = self.dtype == torch.bfloat16 and wide == torch.bfloat16
+        join = (lambda g, u: torch.stack([g, u], dim=1).reshape(2 * g.shape[0], -1)) if self.interleaved \
+            else (lambda g, u: torch.cat([g, u], dim=0))
+        self.gate_up = torch.stack([join(tensors[f"e{e}.gate.weight"].to(wide), tensors[f"e{e}.up.weight"].to(wide))
                                     for e in range(E)]).contiguous()
         self.down = torch.stack([tensors[f"e{e}.down.weight"].to(wide) for e in range(E)]).contiguous()
 
     def kernel_libraries(self) -> Tuple[str, ...]:
-        return ("moe", "gemm_generic")
+        libs = ("moe",) + (kernels.fast_gemm_libraries() if self.interleaved else ())
+        return libs + (self.router.libraries(self.dtype) if self.router is not None else ("gemm_generic",))
 
     def forward(self, step, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True):
         T, d = residual.shape
         E, top, ff = self.n_experts, self.top, self.ff
         P = T * top
         ws = step.ws
-        z = ws.buf("moe_logits", (T, E), torch.float32)
-        kernels.gemm_generic(h, self.router, z)
         ids = ws.buf("moe_ids", (T, top), torch.int32)
         weights = ws.buf("moe_weights", (T, top), torch.float32)
-        kernels.moe_route(z, self.correction, top, self.groups, self.keep_groups, self.group_best, ids, weights,
-                          softmax_scores=self.softmax, renormalize=self.renormalize)
+        route = dict(softmax_scores=self.softmax, renormalize=self.renormalize)
+        if T <= self.SKINNY_TOKENS and h.dtype == self.router.weight.dtype and (3 * E + h.shape[1]) * 4 < 40 * 1024:
+            # few tokens: the router's product is taken inside the routing kernel
+            kernels.moe_route(None, self.correction, top, self.groups, self.keep_groups, self.group_best, ids, weights,
+                              h=h, router=self.router.weight, **route)
+        else:
+            z = ws.buf("moe_logits", (T, E), torch.float32)
+            self.router(h, z)                   # float32 sums of the rows' products (on the tensor cores in bfloat16)
+            kernels.moe_route(z, self.correction, top, self.groups, self.keep_groups, self.group_best, ids, weights,
+                              **route)
         max_tiles = kernels.moe_max_tiles(P, E)
         offs = ws.buf("moe_offs", (E + 1,), torch.int32)
         order = ws.buf("moe_order", (P,), torch.int32)
         tile_expert = ws.buf("moe_tile_expert", (max_tiles,), torch.int32)
         tile_row = ws.buf("moe_tile_row", (max_tiles,), torch.int32)
         n_tiles = ws.buf("moe_n_tiles", (1,), torch.int32)
-        kernels.moe_group(ids.view(-1), E, offs, order, tile_expert, tile_row, n_tiles)
+        place = ws.buf("moe_place", (P,), torch.int32)
+        kernels.moe_group(ids.view(-1), E, offs, order, place, tile_expert, tile_row, n_tiles)
         groups = (offs, order, tile_expert, tile_row, n_tiles)
         act = ws.buf("moe_act", (P, ff), self.dtype)
-        kernels.moe_grouped(h, self.gate_up, act, True, P, top, *groups)
         y = ws.buf("moe_y", (P, d), torch.float32)
-        kernels.moe_grouped(act, self.down, y, False, P, top, *groups)
+        if self.interleaved and T >= self.TENSOR_CORE_TOKENS and self._on_tensor_cores(step, h, offs, order, act, y):
+            kernels.moe_combine(y, weights, residual, accumulate, place=place)
+            return None
+        skinny = T <= self.SKINNY_TOKENS
+        kernels.moe_grouped(h, self.gate_up, act, True, P, top, *groups, interleaved=self.interleaved, skinny=skinny)
+        kernels.moe_grouped(act, self.down, y, False, P, top, *groups, skinny=skinny)
         kernels.moe_combine(y, weights, residual, accumulate)
         return None
+
+    TENSOR_CORE_TOKENS = 128      # from this many tokens on a prompt step's experts run on the tensor cores
+    SKINNY_TOKENS = 64            # up to this many tokens an expert's weights are streamed against its few rows
+
+    def _on_tensor_cores(self, step, h, offs, order, act, y) -> bool:
+        """A prompt step in bfloat16: the tokens' rows are gathered into grouped order and every expert that has
+        rows runs the library's tensor-core product on its run of them (gate/up with the activation in the
+        epilogue, then down into float32 rows in grouped order).  The runs' lengths are known on the device only,
+        so the experts' offsets are read back: one small copy and one wait of the host per layer, which a step of
+        hundreds of tokens hides and a decode step (captured as a graph) never takes."""
+        import ctypes
+        E, top = self.n_experts, self.top
+        P = order.numel()
+        rows = step.ws.buf("moe_rows", (P, h.shape[1]), self.dtype)
+        kernels.moe_gather(h, order, top, rows)
+        if self._host_offs is None:
+            self._host_offs = torch.empty(E + 1, dtype=torch.int32).pin_memory()
+        self._host_offs.copy_(offs, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host = ctypes.c_void_p(self._host_offs.data_ptr())
+        if not kernels.gemm_tc_groups(rows, self.gate_up, act, host, glu="silu"):
+            return False
+        return kernels.gemm_tc_groups(act, self.down, y, host)
 
 
 register_feed_forward("moe", MixtureOfExperts)
