@@ -498,7 +498,7 @@ def run_tumatar(args):
         ms = _timed(lambda: kernels.block_linear(u, gw, gates, bias=gb, epilogue="sigmoid"), args.warmup, args.steps, flush)
         report(f"block_linear (gates of the recurrence, {nb} blocks of {C // nb}), {tag}", "gemm_tc", ms,
                n_tok * C * 2 + n_tok * 2 * C * 4 + gw.numel() * 2, 2.0 * n_tok * 2 * C * (C // nb))
-        proj, taps, cb, lam = bf(n_tok, 2 * C), f32(C, K), f32(C), f32(C)
+        proj, taps, cb, lam = bf(n_tok, 2 * C), f32(K, C), f32(C), f32(C)
         state = torch.zeros(st.n_seqs, K, C, device=dev)
         uo = torch.empty(n_tok, C, dtype=torch.bfloat16, device=dev)
         ms = _timed(lambda: kernels.causal_conv(proj[:, C:], taps, cb, state, st, uo), args.warmup, args.steps, flush)

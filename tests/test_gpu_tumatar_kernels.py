@@ -93,7 +93,7 @@ def test_convolution_and_recurrence_over_steps(dtype, C, K, blocks):
         y = torch.cat([ys[b][used[b]:used[b] + n_] for b, n_ in zip(live, new)])
         proj = torch.cat([y, x], dim=1).contiguous()  # as the part lays them out: [y | x]
         u = torch.empty(st.n_tokens, C, dtype=dtype, device=DEV)
-        kernels.causal_conv(proj[:, C:], taps, cb, state, st, u)
+        kernels.causal_conv(proj[:, C:], taps.t().contiguous(), cb, state, st, u)
         gates = torch.empty(st.n_tokens, 2 * C, dtype=torch.float32, device=DEV)
         kernels.block_linear(u, gw, gates, bias=gb.reshape(-1).contiguous(), epilogue="sigmoid")
         out = torch.empty_like(u)
@@ -124,7 +124,7 @@ def test_long_scan_in_chunks_equals_token_by_token():
             st = _step([n], [0])
             pr = proj[at:at + n].contiguous()
             u = torch.empty(n, C, device=DEV)
-            kernels.causal_conv(pr[:, C:], taps, cb, state, st, u)
+            kernels.causal_conv(pr[:, C:], taps.t().contiguous(), cb, state, st, u)
             gates = torch.empty(n, 2 * C, device=DEV)
             kernels.block_linear(u, gw, gates, bias=gb, epilogue="sigmoid")
             out = torch.empty_like(u)

@@ -146,7 +146,7 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
 // A norm over a row that is a slice of a wider row (x and out with row strides of their own), and the same
 // norm added into a float32 row (the norm behind a sublayer, summed into the residual stream in one pass):
 //   out[r, i] (+)= x[r, i] / sqrt(mean_i x[r, i]^2 + eps) * (w[i] + weight_offset)
-template <typename TW, typename TO, bool ADD>
+template <typename TW, typename TO, bool ADD, bool VEC>
 __global__ void rmsnorm_strided_kernel(const float* __restrict__ x, long x_stride, const TW* __restrict__ w,
                                        TO* __restrict__ out, long out_stride, int d, float eps, float weight_offset) {
     __shared__ float scratch[33];
@@ -155,6 +155,29 @@ __global__ void rmsnorm_strided_kernel(const float* __restrict__ x, long x_strid
     const float* xr = x + (long)blockIdx.x * x_stride;
     TO* o = out + (long)blockIdx.x * out_stride;
     float ss = 0.f;
+    if (VEC) {
+        // the row is a multiple of four long and every pointer and stride keeps sixteen bytes: four at a time
+        const int n4 = d >> 2;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            float ww[4];
+            load4<TW>(w + 4 * i, ww);
+            float y0 = (v.x * inv) * (ww[0] + weight_offset), y1 = (v.y * inv) * (ww[1] + weight_offset);
+            float y2 = (v.z * inv) * (ww[2] + weight_offset), y3 = (v.w * inv) * (ww[3] + weight_offset);
+            if (ADD) {
+                const float4 old = reinterpret_cast<const float4*>(o)[i];
+                y0 += old.x; y1 += old.y; y2 += old.z; y3 += old.w;
+            }
+            store4<TO>(o + 4 * i, y0, y1, y2, y3);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         const float v = xr[i];
         ss = fmaf(v, v, ss);
@@ -350,11 +373,16 @@ ZLM_EXPORT int zlm_rmsnorm_strided(const float* x, long x_stride, const void* w,
                                    cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (d <= 0 || (add && out_dtype != ZLM_F32)) return ZLM_ERR_BAD_ARG;
-    const int threads = norm_threads(d);
+    const int o_el = out_dtype == ZLM_F32 ? 4 : 2;
+    const bool vec = d % 4 == 0 && x_stride % 4 == 0 && (out_stride * o_el) % 16 == 0 && (uintptr_t)x % 16 == 0 &&
+                     (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int threads = vec ? (d >= 2048 ? 256 : (d >= 512 ? 128 : 64)) : norm_threads(d);
     cudaError_t e;
 #define ZLM_NORM_S(TW, TO, ADD)                                                                                      \
-    e = launch_pdl(rmsnorm_strided_kernel<TW, TO, ADD>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, (const TW*)w, \
-                   (TO*)out, out_stride, d, eps, weight_offset)
+    e = vec ? launch_pdl(rmsnorm_strided_kernel<TW, TO, ADD, true>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, \
+                         (const TW*)w, (TO*)out, out_stride, d, eps, weight_offset)                                  \
+            : launch_pdl(rmsnorm_strided_kernel<TW, TO, ADD, false>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, \
+                         (const TW*)w, (TO*)out, out_stride, d, eps, weight_offset)
     if (w_dtype == ZLM_F32 && out_dtype == ZLM_F32) { if (add) ZLM_NORM_S(float, float, true); else ZLM_NORM_S(float, float, false); }
     else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_F32) { if (add) ZLM_NORM_S(__nv_bfloat16, float, true); else ZLM_NORM_S(__nv_bfloat16, float, false); }
     else if (w_dtype == ZLM_F32 && out_dtype == ZLM_BF16) ZLM_NORM_S(float, __nv_bfloat16, false);

@@ -25,7 +25,7 @@ constexpr int GM = 32, GN = 64, GK = 32;
 // row when the router's product is taken here.  z != null: the router logits were computed before.  Otherwise
 // z_e = sum_i h[t, i] * w[e, i] is taken here, a warp per expert with the lanes walking the row in a fixed
 // order (steps of few tokens: a product kernel of its own would cost more than the whole routing).
-constexpr int RT_WARPS = 4;
+constexpr int RT_WARPS = 8;
 
 template <typename TH>
 __global__ void __launch_bounds__(RT_WARPS * 32)
@@ -46,10 +46,21 @@ route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_strid
     } else {
         for (int i = threadIdx.x; i < d; i += blockDim.x) row[i] = to_float(h[(long)t * h_stride + i]);
         __syncthreads();
+        constexpr int V = 16 / (int)sizeof(TH);
+        const bool wide = d % V == 0 && (uintptr_t)w % 16 == 0;
         for (int e = warp; e < E; e += RT_WARPS) {
             const TH* we = w + (long)e * d;
             float acc = 0.f;
-            for (int i = lane; i < d; i += 32) acc = fmaf(row[i], to_float(we[i]), acc);
+            if (wide) {
+                for (int i = lane * V; i < d; i += 32 * V) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(we + i);
+                    const TH* wv = reinterpret_cast<const TH*>(&raw);
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc = fmaf(row[i + k], to_float(wv[k]), acc);
+                }
+            } else {
+                for (int i = lane; i < d; i += 32) acc = fmaf(row[i], to_float(we[i]), acc);
+            }
             acc = warp_sum(acc);
             if (lane == 0) logit[e] = acc;
         }

@@ -1,5 +1,6 @@
 // A gated linear recurrence behind a short causal convolution, per channel:
-//   u_t   = cb + sum_j taps[K-1-j] * x_{t-j}                 (j = 0 is the current token; zeros before the start)
+//   u_t   = cb + sum_j taps[K-1-j] * x_{t-j}                 (j = 0 is the current token; zeros before the start;
+//                                                              taps are kept one row per tap, [K, C])
 //   a_t   = exp(-rate * r_t * softplus(lam)),   r_t, i_t: gates in (0, 1) computed from u_t by the caller
 //   S_t   = a_t * S_{t-1} + sqrt(1 - a_t^2) * i_t * u_t      (S = 0 before the first token, no special case)
 //   out_t = S_t * gelu_tanh(y_t)
@@ -9,7 +10,7 @@
 // when a is close to 1.
 //
 // The recurrence is a composition of affine maps S -> a S + b, which is associative: a block takes one
-// sequence and 32 channels, cuts the sequence's tokens of this step into as many chunks as it has rows of
+// sequence and 32 (or 16) channels, cuts the sequence's tokens of this step into as many chunks as it has rows of
 // threads, every thread composes the maps of its chunk, the chunks' maps are folded in order to give each
 // chunk its incoming state, and a second pass over the chunk writes the outputs.
 #include "common.cuh"
@@ -17,7 +18,8 @@
 namespace zlm {
 
 constexpr int RC_CH = 32;        // channels a block takes
-constexpr int RC_MAX_CHUNKS = 32;
+constexpr int RC_MAX_CHUNKS = 64;
+constexpr int RC_MAX_THREADS = 1024;
 
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -43,7 +45,7 @@ __global__ void conv_kernel(const T* __restrict__ x, long x_stride, const float*
     for (int j = K - 1; j >= 0; --j) {                // oldest input first
         const float xv = (i - j >= 0) ? to_float(x[(long)(t - j) * x_stride + c])
                                       : st[(long)(K - 1 + i - j) * C + c];
-        acc = fmaf(taps[(long)c * K + (K - 1 - j)], xv, acc);
+        acc = fmaf(taps[(long)(K - 1 - j) * C + c], xv, acc);
     }
     u[idx] = from_float<T>(acc);
 }
@@ -81,8 +83,11 @@ __global__ void conv_vec_kernel(const __nv_bfloat16* __restrict__ x, long x_stri
 #pragma unroll
             for (int e = 0; e < 8; ++e) xv[e] = row[e];
         }
+        const float4 w0 = *reinterpret_cast<const float4*>(taps + (long)(K - 1 - j) * C + c);
+        const float4 w1 = *reinterpret_cast<const float4*>(taps + (long)(K - 1 - j) * C + c + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = fmaf(taps[(long)(c + e) * K + (K - 1 - j)], xv[e], acc[e]);
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wv[e], xv[e], acc[e]);
     }
     uint4 o;
     __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -91,9 +96,9 @@ __global__ void conv_vec_kernel(const __nv_bfloat16* __restrict__ x, long x_stri
     *reinterpret_cast<uint4*>(u + (long)t * C + c) = o;
 }
 
-// grid (sequences, ceil(C / 32)), block (32, chunks)
+// grid (sequences, ceil(C / channels a block takes)), block (channels: 32 or 16, chunks)
 template <typename T>
-__global__ void __launch_bounds__(RC_CH * RC_MAX_CHUNKS)
+__global__ void __launch_bounds__(RC_MAX_THREADS)
 scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, int gate_block, const T* __restrict__ y,
             long y_stride, const T* __restrict__ x, long x_stride, const float* __restrict__ lam, float rate,
             float* __restrict__ state, long state_stride, const int* __restrict__ cu_seqlens,
@@ -102,7 +107,7 @@ scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, int gate_b
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
-    const int c = blockIdx.y * RC_CH + threadIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int chunk = threadIdx.y, n_chunks = blockDim.y;
     const int first = cu_seqlens[b], n_new = cu_seqlens[b + 1] - first;
     const int per = (n_new + n_chunks - 1) / n_chunks;
@@ -161,7 +166,8 @@ scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, int gate_b
 
 using namespace zlm;
 
-// x: [T, C] rows with stride x_stride (the convolution's inputs); taps: float [C, K]; bias: float [C];
+// x: [T, C] rows with stride x_stride (the convolution's inputs); taps: float [K, C], the row of the current
+// token last; bias: float [C];
 // state: float [slots, K, C]; u: [T, C] contiguous.
 ZLM_EXPORT int zlm_causal_conv(const void* x, int dtype, long x_stride, const float* taps, const float* bias,
                                const float* state, long state_stride, const int* seq_of_token, const int* cu_seqlens,
@@ -195,10 +201,13 @@ ZLM_EXPORT int zlm_gated_scan(const void* u, int dtype, const float* gates, int 
                               int max_new, int C, int K, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (C <= 0 || K <= 0 || gate_block <= 0 || C % gate_block || max_new <= 0) return ZLM_ERR_BAD_ARG;
-    if ((C + RC_CH - 1) / RC_CH > 65535) return ZLM_ERR_UNSUPPORTED;
+    if ((C + 15) / 16 > 65535) return ZLM_ERR_UNSUPPORTED;
+    // few sequences with many tokens: half as many channels a block and twice the chunks, so that the blocks fill the GPU
+    const int ch = (long)n_seqs * ((C + RC_CH - 1) / RC_CH) < 148 && max_new >= 512 ? RC_CH / 2 : RC_CH;
     int chunks = (max_new + 15) / 16;                 // a chunk of fewer than 16 tokens is not worth a thread
+    if (chunks > RC_MAX_THREADS / ch) chunks = RC_MAX_THREADS / ch;
     if (chunks > RC_MAX_CHUNKS) chunks = RC_MAX_CHUNKS;
-    dim3 grid(n_seqs, (C + RC_CH - 1) / RC_CH), block(RC_CH, chunks);
+    dim3 grid(n_seqs, (C + ch - 1) / ch), block(ch, chunks);
     cudaError_t e;
     if (dtype == ZLM_F32)
         e = launch_pdl(scan_kernel<float>, grid, block, 0, stream, (const float*)u, gates, gate_block, (const float*)y,

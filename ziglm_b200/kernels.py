@@ -322,14 +322,14 @@ def block_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
 
 # ------------------------------------------------------------------- recurrence
 def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, step, u: torch.Tensor) -> None:
-    """u[t, c] = bias[c] + sum_j taps[c, K-1-j] * x[t-j, c] over each sequence of the step; the inputs before the
-    step are rows 0..K-2 of the sequence's state [slots, K, C] (float32; zero for a new sequence).  taps [C, K]
-    and bias [C] are float32; x may be a column slice."""
+    """u[t, c] = bias[c] + sum_j taps[K-1-j, c] * x[t-j, c] over each sequence of the step; the inputs before the
+    step are rows 0..K-2 of the sequence's state [slots, K, C] (float32; zero for a new sequence).  taps [K, C]
+    (one row per tap, the current token's last) and bias [C] are float32; x may be a column slice."""
     _rows(x, "x"); _cuda(u, "u", x.dtype); _cuda(taps, "taps", torch.float32); _cuda(bias, "bias", torch.float32)
     _cuda(state, "state", torch.float32)
     T, C = x.shape
-    K = taps.shape[1]
-    if taps.shape != (C, K) or bias.numel() != C or u.shape != (T, C) or tuple(state.shape[1:]) != (K, C):
+    K = taps.shape[0]
+    if taps.shape != (K, C) or bias.numel() != C or u.shape != (T, C) or tuple(state.shape[1:]) != (K, C):
         raise KernelError("causal_conv: shapes do not match")
     _check(_fn("recurrent", "zlm_causal_conv")(
         x.data_ptr(), code(x.dtype), _row_stride(x), taps.data_ptr(), bias.data_ptr(), state.data_ptr(), state.stride(0),

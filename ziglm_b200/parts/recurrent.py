@@ -53,7 +53,7 @@ class GatedLinearRecurrence(Part):
         bwide = torch.float32 if any(b.dtype == torch.float32 for b in bs) else bs[0].dtype
         self.in_proj = Linear(torch.cat([w.to(wide) for w in ws], dim=0), torch.cat([b.to(bwide) for b in bs], dim=0))
         self.o = Linear(tensors["o.weight"])
-        self.conv_w = tensors["conv.weight"].float().contiguous()
+        self.conv_w = tensors["conv.weight"].float().t().contiguous()          # [taps, channels]: a row per tap
         self.conv_b = tensors["conv.bias"].float().contiguous()
         gw = [tensors["ra.weight"], tensors["ri.weight"]]
         gwide = torch.float32 if any(w.dtype == torch.float32 for w in gw) else gw[0].dtype
