@@ -2,7 +2,7 @@
 prompts, prompts then token by token, prompts in portions down to two tokens, unequal batches with slots and
 pages used again, sequences that end at, before and behind a page border, the first tokens, long decoding,
 greedy generation through ``Engine.generate``, and a replay through ``bin/trace_run``; in float32 and in
-bfloat16, at three configurations that differ in every size.  The recurrences are made to remember for
+bfloat16, at four configurations that differ in every size.  The recurrences are made to remember for
 hundreds of tokens and the routers' choice scores are all negative (tests/tumatar_cases.py: long_memory)."""
 import json
 import os
@@ -44,7 +44,7 @@ def zoo():
     return Zoo()
 
 
-CASES = [(n, d) for n in ("A", "B", "C") for d in DTYPES]
+CASES = [(n, d) for n in ("A", "B", "C", "D") for d in DTYPES]
 
 
 @pytest.mark.parametrize("name,dn", CASES)

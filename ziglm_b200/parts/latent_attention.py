@@ -85,7 +85,7 @@ class LatentAttention(Part):
 
     def kernel_libraries(self) -> Tuple[str, ...]:
         libs = ("elementwise", "block_linear", "attention")
-        libs += kernels.fast_attention_libraries(self.dtype, self.kept, self.n_heads, 1)
+        libs += kernels.fast_attention_libraries(self.dtype, self.kept, min(self.n_heads, self.HEADS_AT_ONCE), 1)
         for lin in (self.down, self.uq, self.o):
             if lin is not None:
                 libs += lin.libraries(self.dtype)
@@ -114,12 +114,23 @@ class LatentAttention(Part):
         kernels.block_linear(q, self.uk_t, qc[:, :H * R])
         kernels.rope_store(qc, H, 1, R, 0, None, step.positions, step.seq_of_token, io.block_table, io.k_pages, None,
                            io.page_size, keys_only=True)
-        mixed = step.ws.buf("lat_mixed", (T, H * R), self.dtype)
-        kernels.attention(step, qc, mixed, H, 1, R, self.scale, None, io)
         heads = step.ws.buf("lat_heads", (T, H * V), self.dtype)
-        kernels.block_linear(mixed, self.uv, heads, epilogue="sigmoid_gate", gate=proj[:, Rq + Rn:])
+        gate = proj[:, Rq + Rn:]
+        # all heads read the one key/value head; the tensor-core kernels take up to 16 query heads a key/value head,
+        # so more heads go through them 16 at a time (the queries are a column slice of the rows, the latent pages
+        # are the same)
+        n = self.HEADS_AT_ONCE if (H > self.HEADS_AT_ONCE and kernels.fast_attention_libraries(
+            self.dtype, R, self.HEADS_AT_ONCE, 1)) else H
+        for h0 in range(0, H, n):
+            h1 = min(H, h0 + n)
+            mixed = step.ws.buf("lat_mixed", (T, (h1 - h0) * R), self.dtype)
+            kernels.attention(step, qc[:, h0 * R:h1 * R], mixed, h1 - h0, 1, R, self.scale, None, io)
+            kernels.block_linear(mixed, self.uv[h0:h1], heads[:, h0 * V:h1 * V], epilogue="sigmoid_gate",
+                                 gate=gate[:, h0 * V:h1 * V])
         self.o(heads, residual, accumulate=accumulate)
         return None
+
+    HEADS_AT_ONCE = 16
 
 
 register_mixer("latent_attention", LatentAttention)
