@@ -10,8 +10,8 @@
 // row (not on the step's other rows or their number):
 //   tiles on the CUDA cores: any sizes, strides and types (the float32 path; the fallback of the other two);
 //   tiles on the tensor cores (mma.sync m16n8k16, bf16 operands): steps of many rows.  The matrices of a block
-//     are small (a head's or a gate block's), so an operand tile is the whole K of 64 rows and the product is
-//     bound by reading x and writing the result; it is kept to warp-level instructions;
+//     are small (a head's or a gate block's, 128 x 128 at the widths of real models), so the product is bound by
+//     reading x and writing the result, and it is kept to warp-level instructions on tiles of 64 x 64 x 64;
 //   a streaming kernel for steps of at most 16 rows: a warp takes an output column, its lanes walk K sixteen
 //     bytes at a time, and the few rows of x come through the cache.
 #include "common.cuh"
