@@ -55,13 +55,15 @@ CFG_C = {
         {"type": "latent_attention", "mixer": _lat(2, 32, 32, 16, 64, 1.0), "mlp": {"kind": "dense", "ff": 96, "limit": 1.5}},
     ],
 }
-# more heads than the tensor-core attention takes on one key/value head (they go through it 16 at a time)
+# more heads than the tensor-core attention takes on one key/value head (they go through it 16 at a time), and
+# sizes that are no multiple of 8 anywhere (head 12, value 6, query latent 20, 42 channels in blocks of 14): the
+# kernels that move sixteen bytes at a time step aside for the ones that take any size
 CFG_D = {
     "architecture": "Tumatar", "vocab": 150, "width": 64, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
     "logit_scale": 1.0,
     "layers": [
-        {"type": "latent_attention", "mixer": _lat(20, 16, 8, 32, 64, 0.5), "mlp": {"kind": "dense", "ff": 72, "limit": 3.0}},
-        {"type": "rglru", "mixer": {"width": 48, "blocks": 3, "conv": 5}},
+        {"type": "latent_attention", "mixer": _lat(20, 12, 6, 20, 64, 0.5), "mlp": {"kind": "dense", "ff": 76, "limit": 3.0}},
+        {"type": "rglru", "mixer": {"width": 42, "blocks": 3, "conv": 5}, "mlp": _moe(20, 3, 2, 1, 1)},
     ],
 }
 CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D}

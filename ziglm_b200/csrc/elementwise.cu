@@ -191,6 +191,41 @@ __global__ void rmsnorm_strided_kernel(const float* __restrict__ x, long x_strid
     }
 }
 
+// The norm behind a sublayer, the residual sum and the norm before the next sublayer in one pass over a row:
+//   x[r] += branch[r] / rms(branch[r]) * (w1 + off1);   h[r] = x[r] / rms(x[r]) * (w2 + off2)
+// The new row of x stays in shared memory between the two norms (d floats of dynamic shared memory).
+template <typename TW, typename TO>
+__global__ void norm_add_norm_kernel(const float* __restrict__ branch, const TW* __restrict__ w1, float off1, float eps1,
+                                     float* __restrict__ x, const TW* __restrict__ w2, float off2, float eps2,
+                                     TO* __restrict__ h, int d) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* br = branch + (long)blockIdx.x * d;
+    float* xr = x + (long)blockIdx.x * d;
+    TO* hr = h + (long)blockIdx.x * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = br[i];
+        row[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv1 = 1.0f / sqrtf(ss / (float)d + eps1);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i] + (row[i] * inv1) * (to_float(w1[i]) + off1);
+        xr[i] = v;
+        row[i] = v;
+        ss2 = fmaf(v, v, ss2);
+    }
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.0f / sqrtf(ss2 / (float)d + eps2);
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        hr[i] = from_float<TO>((row[i] * inv2) * (to_float(w2[i]) + off2));
+}
+
 // x[t, :] += table[row, :] for every row t of x (a learned vector added to the whole step)
 template <typename TW>
 __global__ void add_row_kernel(float* __restrict__ x, const TW* __restrict__ table_row, long total, int d) {
@@ -389,6 +424,28 @@ ZLM_EXPORT int zlm_rmsnorm_strided(const float* x, long x_stride, const void* w,
     else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_BF16) ZLM_NORM_S(__nv_bfloat16, __nv_bfloat16, false);
     else return ZLM_ERR_UNSUPPORTED;
 #undef ZLM_NORM_S
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// branch, x: float [n_rows, d] contiguous; h: [n_rows, d] in out_dtype; w1, w2 of one type.
+ZLM_EXPORT int zlm_norm_add_norm(const float* branch, const void* w1, float off1, float eps1, float* x, const void* w2,
+                                 float off2, float eps2, int w_dtype, void* h, int out_dtype, int n_rows, int d,
+                                 cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) return ZLM_ERR_BAD_ARG;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 40 * 1024) return ZLM_ERR_UNSUPPORTED;
+    const int threads = norm_threads(d);
+    cudaError_t e;
+#define ZLM_NAN(TW, TO)                                                                                          \
+    e = launch_pdl(norm_add_norm_kernel<TW, TO>, dim3(n_rows), dim3(threads), smem, stream, branch, (const TW*)w1, off1, \
+                   eps1, x, (const TW*)w2, off2, eps2, (TO*)h, d)
+    if (w_dtype == ZLM_F32 && out_dtype == ZLM_F32) ZLM_NAN(float, float);
+    else if (w_dtype == ZLM_F32 && out_dtype == ZLM_BF16) ZLM_NAN(float, __nv_bfloat16);
+    else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_F32) ZLM_NAN(__nv_bfloat16, float);
+    else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_BF16) ZLM_NAN(__nv_bfloat16, __nv_bfloat16);
+    else return ZLM_ERR_UNSUPPORTED;
+#undef ZLM_NAN
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 

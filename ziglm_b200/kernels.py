@@ -55,6 +55,8 @@ _PROTOTYPES = {
         "zlm_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
         "zlm_rmsnorm_strided": [c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_long, c_int, c_int, c_int, c_float,
                                 c_float, c_void_p],
+        "zlm_norm_add_norm": [c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p,
+                              c_int, c_int, c_int, c_void_p],
         "zlm_add_row": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "zlm_scale": [c_void_p, c_long, c_float, c_void_p],
         "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
@@ -267,6 +269,25 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: 
     _check(_fn("elementwise", "zlm_rmsnorm_strided")(
         x.data_ptr(), _row_stride(x), weight.data_ptr(), code(weight.dtype), out.data_ptr(), code(out.dtype),
         _row_stride(out), int(add), n, d, eps, weight_offset, _stream()), "rmsnorm_rows")
+
+
+def norm_add_norm(branch: torch.Tensor, w1: torch.Tensor, eps1: float, x: torch.Tensor, w2: torch.Tensor, eps2: float,
+                  h: torch.Tensor, off1: float = 0.0, off2: float = 0.0) -> bool:
+    """x += rmsnorm(branch; w1, eps1) and h = rmsnorm(x; w2, eps2) in one pass over each row: the norm behind a
+    sublayer, the residual sum and the norm before the next sublayer.  branch and x float32 [n, d] contiguous; h
+    [n, d] in its own type; w1 and w2 of one type.  False, having done nothing, for rows too long for the kernel's
+    shared memory."""
+    _cuda(branch, "branch", torch.float32); _cuda(x, "x", torch.float32); _cuda(h, "h"); _cuda(w1, "w1"); _cuda(w2, "w2", w1.dtype)
+    n, d = x.shape
+    if branch.shape != (n, d) or h.shape != (n, d) or w1.numel() != d or w2.numel() != d:
+        raise KernelError("norm_add_norm: shapes do not match")
+    status = _fn("elementwise", "zlm_norm_add_norm")(branch.data_ptr(), w1.data_ptr(), float(off1), float(eps1), x.data_ptr(),
+                                                     w2.data_ptr(), float(off2), float(eps2), code(w1.dtype), h.data_ptr(),
+                                                     code(h.dtype), n, d, _stream())
+    if status == -2:
+        return False
+    _check(status, "norm_add_norm")
+    return True
 
 
 def add_row(x: torch.Tensor, row: torch.Tensor) -> None:

@@ -87,7 +87,8 @@ class SandwichBlock(Part):
     has no feed-forward (``ffn`` and ``ffn_norm`` are None) ends after the mixer.  A sublayer writes its output
     into a float32 branch buffer of the step's scratch (a part that sets ``can_overwrite`` is asked to overwrite
     it, for any other the buffer is zeroed first and the part adds into it, as it would into the residual); the
-    post-norm then reads the branch in float32 and adds the normed rows into the residual in the same kernel.
+    post-norm then reads the branch in float32 and adds the normed rows into the residual in the same kernel,
+    which also leaves the rows of the norm before the next sublayer (of this block or of the next one).
     """
 
     def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
@@ -140,7 +141,8 @@ class SandwichBlock(Part):
         return self.mixer.state_needs()
 
     def accepts_normed_input(self) -> bool:
-        return False
+        """The block before may hand this block's first norm over as finished rows (``h_in``)."""
+        return bool(self.mixer_norm.fusable)
 
     @staticmethod
     def _branch(step, part, x: torch.Tensor) -> torch.Tensor:
@@ -149,23 +151,35 @@ class SandwichBlock(Part):
             branch.zero_()
         return branch
 
+    def _close(self, step, post, branch: torch.Tensor, x: torch.Tensor, nxt, name: str):
+        """x += post(branch); with ``nxt`` (the norm of the sublayer that follows, here or in the next block) also
+        its rows of the new x, from the same kernel.  Returns those rows or None."""
+        if nxt is not None and hasattr(post, "add_normed_then") and getattr(nxt, "fusable", False):
+            return post.add_normed_then(step, branch, x, nxt, name=name)
+        post.add_normed(step, branch, x)
+        return None
+
     def forward(self, step, io: LayerIO, x: torch.Tensor, h_in=None, next_norm=None):
-        h = self.mixer_norm.forward(step, x)
+        """``h_in``: this block's first norm, done by the block before (finished rows; a half-done norm of the
+        kind the products of a pre-norm block carry is not taken).  ``next_norm``: the first norm of the block
+        after; the result is its rows if this block's last kernel made them, else None."""
+        h = h_in if isinstance(h_in, torch.Tensor) else self.mixer_norm.forward(step, x)
         branch = self._branch(step, self.mixer, x)
         if self.mixer.can_overwrite:
             self.mixer.forward(step, io, h, branch, accumulate=False)
         else:
             self.mixer.forward(step, io, h, branch)
-        self.mixer_post.add_normed(step, branch, x)
-        if self.ffn is not None:
+        if self.ffn is None:
+            return self._close(step, self.mixer_post, branch, x, next_norm, "norm_out_next")
+        h = self._close(step, self.mixer_post, branch, x, self.ffn_norm, "norm_out_ffn")
+        if h is None:
             h = self.ffn_norm.forward(step, x)
-            branch = self._branch(step, self.ffn, x)
-            if self.ffn.can_overwrite:
-                self.ffn.forward(step, h, branch, accumulate=False)
-            else:
-                self.ffn.forward(step, h, branch)
-            self.ffn_post.add_normed(step, branch, x)
-        return None
+        branch = self._branch(step, self.ffn, x)
+        if self.ffn.can_overwrite:
+            self.ffn.forward(step, h, branch, accumulate=False)
+        else:
+            self.ffn.forward(step, h, branch)
+        return self._close(step, self.ffn_post, branch, x, next_norm, "norm_out_next")
 
 
 register_block("sandwich", SandwichBlock)

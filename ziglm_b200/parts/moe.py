@@ -110,10 +110,13 @@ class MixtureOfExperts(Part):
         groups = (offs, order, tile_expert, tile_row, n_tiles)
         act = ws.buf("moe_act", (P, ff), self.dtype)
         y = ws.buf("moe_y", (P, d), torch.float32)
-        if self.interleaved and T >= self.TENSOR_CORE_TOKENS and self._on_tensor_cores(step, h, offs, order, act, y):
+        # a step of one token a sequence may be captured as a graph, whatever its size: nothing is read back in it
+        single = bool(getattr(step, "single_token", False))
+        if (self.interleaved and T >= self.TENSOR_CORE_TOKENS and not single
+                and self._on_tensor_cores(step, h, offs, order, act, y)):
             kernels.moe_combine(y, weights, residual, accumulate, place=place)
             return None
-        skinny = T <= self.SKINNY_TOKENS
+        skinny = T <= self.SKINNY_TOKENS or single
         kernels.moe_grouped(h, self.gate_up, act, True, P, top, *groups, interleaved=self.interleaved, skinny=skinny)
         kernels.moe_grouped(act, self.down, y, False, P, top, *groups, skinny=skinny)
         kernels.moe_combine(y, weights, residual, accumulate)

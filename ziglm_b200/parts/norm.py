@@ -50,6 +50,18 @@ class RMSNorm(Part):
         stream by the kernel that takes it."""
         kernels.rmsnorm_rows(branch, self.weight, residual, self.eps, add=True, weight_offset=self.weight_offset)
 
+    def add_normed_then(self, step, branch: torch.Tensor, residual: torch.Tensor, nxt: "RMSNorm",
+                        name: str = "norm_out") -> torch.Tensor:
+        """residual += norm(branch), and the rows of the norm ``nxt`` of the new residual (the input of the next
+        sublayer), in one kernel where the row fits its shared memory, else in two."""
+        out = step.ws.buf(name, tuple(residual.shape), self.dtype)
+        if (isinstance(nxt, RMSNorm) and nxt.weight.dtype == self.weight.dtype
+                and kernels.norm_add_norm(branch, self.weight, self.eps, residual, nxt.weight, nxt.eps, out,
+                                          off1=self.weight_offset, off2=nxt.weight_offset)):
+            return out
+        self.add_normed(step, branch, residual)
+        return nxt.forward(step, residual, out=out)
+
     def forward_rows(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """The norm of float32 rows that may be a column slice of a wider matrix, into rows that may be one too."""
         kernels.rmsnorm_rows(x, self.weight, out, self.eps, weight_offset=self.weight_offset)
