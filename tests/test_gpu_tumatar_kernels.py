@@ -198,6 +198,24 @@ def test_clamped_activation_and_the_norm_that_adds(dtype):
     torch.testing.assert_close(res, want, atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,d", [(1, 24), (37, 200), (5, 4096)])
+def test_norm_sum_norm_in_one_kernel(dtype, T, d):
+    """x += norm1(branch); h = norm2(x) against the two norms taken one after the other."""
+    from ziglm_b200 import kernels
+    branch, x = _r(T, d, seed=1, scale=3.0), _r(T, d, seed=2)
+    w1, w2 = _r(d, seed=3, dtype=dtype) + 1.0, _r(d, seed=4, dtype=dtype) + 1.0
+    want_x = x.cpu() + P.rms_norm(branch.cpu(), w1.cpu(), 1e-5)
+    want_h = P.rms_norm(want_x, w2.cpu(), 1e-6)
+    h = torch.empty(T, d, dtype=dtype, device=DEV)
+    assert kernels.norm_add_norm(branch, w1, 1e-5, x, w2, 1e-6, h)
+    torch.testing.assert_close(x.cpu(), want_x, atol=1e-5, rtol=1e-5)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(h.float().cpu(), want_h, **tol)
+    assert not kernels.norm_add_norm(_r(2, 20000, seed=5), _r(20000, seed=6, dtype=dtype), 1e-5, _r(2, 20000, seed=7),
+                                     _r(20000, seed=8, dtype=dtype), 1e-5, torch.empty(2, 20000, dtype=dtype, device=DEV))
+
+
 @pytest.mark.parametrize("dtype,R,H", [(torch.float32, 320, 2), (torch.float32, 40, 3), (torch.bfloat16, 128, 7),
                                        (torch.bfloat16, 64, 16), (torch.bfloat16, 200, 4)])
 def test_attention_over_a_latent_that_is_key_and_value(dtype, R, H):

@@ -116,14 +116,15 @@ class MixtureOfExperts(Part):
                 and self._on_tensor_cores(step, h, offs, order, act, y)):
             kernels.moe_combine(y, weights, residual, accumulate, place=place)
             return None
-        skinny = T <= self.SKINNY_TOKENS or single
+        skinny = T <= self.SKINNY_TOKENS or single or (self.interleaved and T < self.TENSOR_CORE_TOKENS)
         kernels.moe_grouped(h, self.gate_up, act, True, P, top, *groups, interleaved=self.interleaved, skinny=skinny)
         kernels.moe_grouped(act, self.down, y, False, P, top, *groups, skinny=skinny)
         kernels.moe_combine(y, weights, residual, accumulate)
         return None
 
     TENSOR_CORE_TOKENS = 128      # from this many tokens on a prompt step's experts run on the tensor cores
-    SKINNY_TOKENS = 64            # up to this many tokens an expert's weights are streamed against its few rows
+    SKINNY_TOKENS = 64            # up to this many tokens (in bfloat16: up to where the tensor cores take over, and in
+                                  # every step of one token a sequence) an expert's weights are streamed against its rows
 
     def _on_tensor_cores(self, step, h, offs, order, act, y) -> bool:
         """A prompt step in bfloat16: the tokens' rows are gathered into grouped order and every expert that has
