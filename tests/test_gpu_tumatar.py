@@ -225,3 +225,21 @@ def test_replay_from_a_folder(tmp_path):
                 TC.rows_close(got, want[0][i:i + 1], dn, f"replay, token {i}")
         finally:
             rp.close()
+
+
+@pytest.mark.parametrize("kind", ["rglru", "latent_attention"])
+def test_a_model_of_one_kind_of_mixer(kind):
+    """Only recurrences (no cache group at all: nothing but state is kept) and only attention (no state): the
+    same layer three times in a row through a loop of one layer."""
+    cfg = TC.config("B")
+    layer = [l for l in cfg["layers"] if l["type"] == kind][0]
+    cfg["layers"] = [layer]
+    cfg["loop"] = {"start": 0, "stop": 1, "times": 3}
+    eng, cfg, w = TC.build(cfg, 21, "float32")
+    assert (len(eng.cache.groups) == 0) == (kind == "rglru") and (len(eng.cache.states) == 0) == (kind != "rglru")
+    r = random_tokens(90, cfg["vocab"], 77)
+    want = P.forward(cfg, w, r)
+    s = eng.alloc_slot()
+    rows = [eng.step([(s, r[:70])], [list(range(70))]).clone()] + [eng.step([(s, [t])]).clone() for t in r[70:]]
+    eng.free_slot(s)
+    TC.rows_close(torch.cat(rows), want, "float32", f"only {kind}")

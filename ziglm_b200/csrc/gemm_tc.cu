@@ -1122,7 +1122,7 @@ ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int b
 // offsets are host memory: the caller has read them back.  A group without rows launches nothing.  A group's
 // product is small (a few hundred rows) and fills a fraction of the GPU, so the groups are dealt out over a few
 // streams of this library that fork from `stream` and join it again; they write disjoint rows.
-constexpr int GROUP_STREAMS = 4;
+constexpr int GROUP_STREAMS = 8;
 
 ZLM_EXPORT int zlm_gemm_tc_groups(const void* X, const void* W, void* Y, int y_dtype, int glu, const int* host_offs,
                                   int n_groups, int N, int K, long ldx, long ldw, long ldy, long w_group_stride,
