@@ -8,6 +8,7 @@
     python bench.py --case workload-13b     8 prompts of 2,048 tokens, then 256 steps (13B shape)
     python bench.py --case float32 [--layers L]    the 8B shape in true 32-bit: a 2,048-token prompt, decode at batch 1 and 8
     python bench.py --case reference-kernels [--context C]     the reference's CUDA kernels alone, if they were built
+    python bench.py --case tumatar [--shape 1b|8b] [--layers L]    the Tumatar design beside Llama at equal width, its kernels alone
 
 A "step" is one decode step of a batch of 8 sequences at a context of 4096
 tokens.  ``value`` is decoded tokens a second, timed on the device with CUDA
