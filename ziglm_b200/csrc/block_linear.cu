@@ -104,8 +104,13 @@ __global__ void __launch_bounds__(128)
 block_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long x_stride, const __nv_bfloat16* __restrict__ w,
                         const float* __restrict__ bias, TO* __restrict__ out, long out_stride, int T, int N, int K, int epi,
                         const float* __restrict__ gate, long gate_stride) {
-    __shared__ __align__(16) __nv_bfloat16 xs[MM_BM][MM_KC + MM_PAD];
-    __shared__ __align__(16) __nv_bfloat16 wsm[MM_BN][MM_KC + MM_PAD];
+    // operand tiles; when the products are done the same memory stages the tile's sums on their way out
+    constexpr int LDS = MM_KC + MM_PAD, LDO = MM_BN + 1;
+    __shared__ __align__(16) unsigned char raw[2 * MM_BM * LDS * 2];
+    static_assert(sizeof(float) * MM_BM * LDO <= sizeof(raw), "the staged sums must fit the operand tiles");
+    __nv_bfloat16 (*xs)[LDS] = reinterpret_cast<__nv_bfloat16 (*)[LDS]>(raw);
+    __nv_bfloat16 (*wsm)[LDS] = reinterpret_cast<__nv_bfloat16 (*)[LDS]>(raw + MM_BM * LDS * 2);
+    float* stage = reinterpret_cast<float*>(raw);
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.z, n0 = blockIdx.x * MM_BN, t0 = blockIdx.y * MM_BM;
@@ -146,14 +151,51 @@ block_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long x_stride, cons
         }
         __syncthreads();
     }
+    // the sums go through shared memory so that a thread writes eight neighbours of a row at once
 #pragma unroll
     for (int j = 0; j < MM_BN / 8; ++j)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int t = t0 + warp * 16 + g + (i >= 2 ? 8 : 0);
-            const int n = n0 + j * 8 + 2 * q + (i & 1);
-            if (t < T && n < N) bl_store<TO>(out, out_stride, t, (long)b * N + n, acc[j][i], bias, epi, gate, gate_stride);
+        for (int i = 0; i < 4; ++i)
+            stage[(warp * 16 + g + (i >= 2 ? 8 : 0)) * LDO + j * 8 + 2 * q + (i & 1)] = acc[j][i];
+    __syncthreads();
+    const bool wide = out_stride % 8 == 0 && ((long)b * N + n0) % 8 == 0 && (uintptr_t)out % 16 == 0 &&
+                      (epi != 2 || (gate_stride % 4 == 0 && (uintptr_t)gate % 16 == 0));
+    for (int idx = threadIdx.x; idx < MM_BM * (MM_BN / 8); idx += 128) {
+        const int r = idx / (MM_BN / 8), c8 = (idx % (MM_BN / 8)) * 8;
+        const int t = t0 + r;
+        if (t >= T || n0 + c8 >= N) continue;
+        const long col = (long)b * N + n0 + c8;
+        if (wide && n0 + c8 + 8 <= N) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[e] = stage[r * LDO + c8 + e];
+                if (bias) v[e] += bias[col + e];
+                if (epi == 1) v[e] = 1.0f / (1.0f + expf(-v[e]));
+            }
+            if (epi == 2) {
+                const float4 g0 = *reinterpret_cast<const float4*>(gate + (long)t * gate_stride + col);
+                const float4 g1 = *reinterpret_cast<const float4*>(gate + (long)t * gate_stride + col + 4);
+                const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = round_to<TO>(v[e]) * (1.0f / (1.0f + expf(-gv[e])));
+            }
+            TO* o = out + (long)t * out_stride + col;
+            if (sizeof(TO) == 2) {
+                uint4 pk;
+                __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ph[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                *reinterpret_cast<uint4*>(o) = pk;
+            } else {
+                *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        } else {
+            for (int e = 0; e < 8 && n0 + c8 + e < N; ++e)
+                bl_store<TO>(out, out_stride, t, col + e, stage[r * LDO + c8 + e], bias, epi, gate, gate_stride);
         }
+    }
 }
 
 // ------------------------------------------------------------------ few rows
