@@ -168,16 +168,18 @@ __global__ void group_kernel(const int* __restrict__ ids, int P, int E, int* __r
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     __syncthreads();
     if (P <= 1024) {
-        // few pairs: a stable order, so that a row's place does not depend on the timing of the threads
-        if (threadIdx.x < E) {
-            int at = start[threadIdx.x];
-            for (int p = 0; p < P; ++p)
-                if (ids[p] == (int)threadIdx.x) { place[p] = at; sorted[at++] = p; }
-        }
-        for (int e = blockDim.x + threadIdx.x; e < E; e += blockDim.x) {
-            int at = start[e];
-            for (int p = 0; p < P; ++p)
-                if (ids[p] == e) { place[p] = at; sorted[at++] = p; }
+        // few pairs: a stable order (pairs of an expert in ascending order), so that a row's place does not depend
+        // on the timing of the threads.  A pair's rank is the number of earlier pairs of its expert.
+        int* cached = start + E + 1;          // [P]
+        for (int p = threadIdx.x; p < P; p += blockDim.x) cached[p] = ids[p];
+        __syncthreads();
+        for (int p = threadIdx.x; p < P; p += blockDim.x) {
+            const int e = cached[p];
+            int rank = 0;
+            for (int q = 0; q < p; ++q) rank += cached[q] == e ? 1 : 0;
+            const int at = start[e] + rank;
+            sorted[at] = p;
+            place[p] = at;
         }
     } else {
         for (int p = threadIdx.x; p < P; p += blockDim.x) {
@@ -428,7 +430,7 @@ ZLM_EXPORT int zlm_moe_group(const int* ids, int P, int E, int* offs, int* sorte
                              int* tile_row, int* n_tiles, cudaStream_t stream) {
     if (P <= 0) return 0;
     if (E <= 0) return ZLM_ERR_BAD_ARG;
-    const size_t smem = (2 * (size_t)E + 1) * sizeof(int);
+    const size_t smem = (2 * (size_t)E + 1 + (P <= 1024 ? P : 0)) * sizeof(int);
     if (smem > 48 * 1024) return ZLM_ERR_UNSUPPORTED;
     cudaError_t e = launch_pdl(group_kernel, dim3(1), dim3(1024), smem, stream, ids, P, E, offs, sorted, place,
                                tile_expert, tile_row, n_tiles);
