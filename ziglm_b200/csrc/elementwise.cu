@@ -155,7 +155,7 @@ __global__ void rmsnorm_strided_kernel(const float* __restrict__ x, long x_strid
     const float* xr = x + (long)blockIdx.x * x_stride;
     TO* o = out + (long)blockIdx.x * out_stride;
     float ss = 0.f;
-    if (VEC) {
+    if constexpr (VEC) {
         // the row is a multiple of four long and every pointer and stride keeps sixteen bytes: four at a time
         const int n4 = d >> 2;
         for (int i = threadIdx.x; i < n4; i += blockDim.x) {
@@ -176,54 +176,88 @@ __global__ void rmsnorm_strided_kernel(const float* __restrict__ x, long x_strid
             }
             store4<TO>(o + 4 * i, y0, y1, y2, y3);
         }
-        return;
-    }
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = xr[i];
-        ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float y = (xr[i] * inv) * (to_float(w[i]) + weight_offset);
-        if (ADD) o[i] = from_float<TO>(to_float(o[i]) + y);
-        else o[i] = from_float<TO>(y);
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = xr[i];
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float y = (xr[i] * inv) * (to_float(w[i]) + weight_offset);
+            if (ADD) o[i] = from_float<TO>(to_float(o[i]) + y);
+            else o[i] = from_float<TO>(y);
+        }
     }
 }
 
 // The norm behind a sublayer, the residual sum and the norm before the next sublayer in one pass over a row:
 //   x[r] += branch[r] / rms(branch[r]) * (w1 + off1);   h[r] = x[r] / rms(x[r]) * (w2 + off2)
 // The new row of x stays in shared memory between the two norms (d floats of dynamic shared memory).
-template <typename TW, typename TO>
+template <typename TW, typename TO, bool VEC>
 __global__ void norm_add_norm_kernel(const float* __restrict__ branch, const TW* __restrict__ w1, float off1, float eps1,
                                      float* __restrict__ x, const TW* __restrict__ w2, float off2, float eps2,
                                      TO* __restrict__ h, int d) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
     const float* br = branch + (long)blockIdx.x * d;
     float* xr = x + (long)blockIdx.x * d;
     TO* hr = h + (long)blockIdx.x * d;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = br[i];
-        row[i] = v;
-        ss = fmaf(v, v, ss);
+    if constexpr (VEC) {
+        // d is a multiple of four and every pointer keeps sixteen bytes: four elements at a time
+        const int n4 = d >> 2;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(br)[i];
+            reinterpret_cast<float4*>(row)[i] = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv1 = 1.0f / sqrtf(ss / (float)d + eps1);
+        float ss2 = 0.f;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 b4 = reinterpret_cast<const float4*>(row)[i];
+            float4 v = reinterpret_cast<const float4*>(xr)[i];
+            float ww[4];
+            load4<TW>(w1 + 4 * i, ww);
+            v.x += (b4.x * inv1) * (ww[0] + off1); v.y += (b4.y * inv1) * (ww[1] + off1);
+            v.z += (b4.z * inv1) * (ww[2] + off1); v.w += (b4.w * inv1) * (ww[3] + off1);
+            reinterpret_cast<float4*>(xr)[i] = v;
+            reinterpret_cast<float4*>(row)[i] = v;
+            ss2 = fmaf(v.x, v.x, ss2); ss2 = fmaf(v.y, v.y, ss2); ss2 = fmaf(v.z, v.z, ss2); ss2 = fmaf(v.w, v.w, ss2);
+        }
+        ss2 = block_sum(ss2, scratch);
+        const float inv2 = 1.0f / sqrtf(ss2 / (float)d + eps2);
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(row)[i];
+            float ww[4];
+            load4<TW>(w2 + 4 * i, ww);
+            store4<TO>(hr + 4 * i, (v.x * inv2) * (ww[0] + off2), (v.y * inv2) * (ww[1] + off2),
+                       (v.z * inv2) * (ww[2] + off2), (v.w * inv2) * (ww[3] + off2));
+        }
+    } else {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = br[i];
+            row[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv1 = 1.0f / sqrtf(ss / (float)d + eps1);
+        float ss2 = 0.f;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = xr[i] + (row[i] * inv1) * (to_float(w1[i]) + off1);
+            xr[i] = v;
+            row[i] = v;
+            ss2 = fmaf(v, v, ss2);
+        }
+        ss2 = block_sum(ss2, scratch);
+        const float inv2 = 1.0f / sqrtf(ss2 / (float)d + eps2);
+        for (int i = threadIdx.x; i < d; i += blockDim.x)
+            hr[i] = from_float<TO>((row[i] * inv2) * (to_float(w2[i]) + off2));
     }
-    ss = block_sum(ss, scratch);
-    const float inv1 = 1.0f / sqrtf(ss / (float)d + eps1);
-    float ss2 = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = xr[i] + (row[i] * inv1) * (to_float(w1[i]) + off1);
-        xr[i] = v;
-        row[i] = v;
-        ss2 = fmaf(v, v, ss2);
-    }
-    ss2 = block_sum(ss2, scratch);
-    const float inv2 = 1.0f / sqrtf(ss2 / (float)d + eps2);
-    for (int i = threadIdx.x; i < d; i += blockDim.x)
-        hr[i] = from_float<TO>((row[i] * inv2) * (to_float(w2[i]) + off2));
 }
 
 // x[t, :] += table[row, :] for every row t of x (a learned vector added to the whole step)
@@ -435,11 +469,15 @@ ZLM_EXPORT int zlm_norm_add_norm(const float* branch, const void* w1, float off1
     if (d <= 0) return ZLM_ERR_BAD_ARG;
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 40 * 1024) return ZLM_ERR_UNSUPPORTED;
-    const int threads = norm_threads(d);
+    const bool vec = d % 4 == 0 && (uintptr_t)branch % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)h % 16 == 0 &&
+                     (uintptr_t)w1 % 16 == 0 && (uintptr_t)w2 % 16 == 0;
+    const int threads = vec ? (d >= 2048 ? 256 : (d >= 512 ? 128 : 64)) : norm_threads(d);
     cudaError_t e;
 #define ZLM_NAN(TW, TO)                                                                                          \
-    e = launch_pdl(norm_add_norm_kernel<TW, TO>, dim3(n_rows), dim3(threads), smem, stream, branch, (const TW*)w1, off1, \
-                   eps1, x, (const TW*)w2, off2, eps2, (TO*)h, d)
+    e = vec ? launch_pdl(norm_add_norm_kernel<TW, TO, true>, dim3(n_rows), dim3(threads), smem, stream, branch,    \
+                         (const TW*)w1, off1, eps1, x, (const TW*)w2, off2, eps2, (TO*)h, d)                     \
+            : launch_pdl(norm_add_norm_kernel<TW, TO, false>, dim3(n_rows), dim3(threads), smem, stream, branch,   \
+                         (const TW*)w1, off1, eps1, x, (const TW*)w2, off2, eps2, (TO*)h, d)
     if (w_dtype == ZLM_F32 && out_dtype == ZLM_F32) ZLM_NAN(float, float);
     else if (w_dtype == ZLM_F32 && out_dtype == ZLM_BF16) ZLM_NAN(float, __nv_bfloat16);
     else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_F32) ZLM_NAN(__nv_bfloat16, float);
