@@ -15,6 +15,7 @@ from typing import Any, Callable, Dict, Mapping
 from .common import ConfigError, architecture_name, read_config_json
 from .llama import LlamaConfig
 from .tumatar import TumatarConfig
+from .tikalix import TikalixConfig
 from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -64,3 +65,4 @@ def config_from_folder(folder: str):
 
 register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
 register_architecture(TumatarConfig.ARCHITECTURE, TumatarConfig)
+register_architecture(TikalixConfig.ARCHITECTURE, TikalixConfig)

@@ -77,10 +77,10 @@ class LayerSpec:
     arrangement reads none."""
     block: str                     # registry key of the arrangement, e.g. "prenorm"
     prefix: str                    # tensor-name prefix of this layer's weights
-    mixer_norm: NormSpec
+    mixer_norm: Optional[NormSpec] # None: the arrangement has no norm before the mixer (it reads the residual itself)
     mixer: MixerSpec
-    ffn_norm: Optional[NormSpec]   # None together with ``ffn``: the layer has no feed-forward
-    ffn: Optional[FeedForwardSpec]
+    ffn_norm: Optional[NormSpec]   # None: no norm before the feed-forward, or no feed-forward
+    ffn: Optional[FeedForwardSpec] # None: the layer has no feed-forward
     # local parameter name (as the part declares it) -> name under ``prefix``
     names: Mapping[str, str] = field(default_factory=dict)
     options: Mapping[str, Any] = field(default_factory=dict)
@@ -125,8 +125,11 @@ class ModelSpec:
             src = layer.mixer.cache_from
             if src is not None and not 0 <= src < len(self.layers):
                 raise ValueError(f"layer {i} reads the cache of layer {src}, which does not exist")
-            if (layer.ffn is None) != (layer.ffn_norm is None):
-                raise ValueError(f"layer {i}: a feed-forward and its norm come together or not at all")
+            if layer.ffn is None and layer.ffn_norm is not None:
+                raise ValueError(f"layer {i}: a norm before a feed-forward that the layer does not have")
+            if layer.block in ("prenorm", "sandwich") and (layer.mixer_norm is None or
+                                                           (layer.ffn is not None and layer.ffn_norm is None)):
+                raise ValueError(f"layer {i}: the {layer.block} arrangement needs a norm before each sublayer")
         for place in self.place_hooks:
             if not 0 <= place < len(self.schedule):
                 raise ValueError(f"a hook is hung before place {place}, but the schedule has {len(self.schedule)} places")

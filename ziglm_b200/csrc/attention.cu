@@ -35,6 +35,7 @@ namespace zlm {
 // k (rotated) and v heads are copied to the token's row of the cache pages.
 // qkv row layout: [q: n_heads*hd | k: n_kv*hd | v: n_kv*hd]
 constexpr int ROPE_MAX_HALF = 256;
+constexpr int ATT_MAX_HD_ROPE = 512;     // the largest head the norming rotation takes
 
 template <typename T>
 __global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
@@ -184,6 +185,97 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_
     }
 }
 
+// Rotation with an amplitude, a unit RMS norm of every rotated query and key head, and the cache write.
+// One warp per head at a time: the head is read into shared memory as floats, its first `rot` dimensions are
+// turned (cosines and sines times `amplitude`), the head is divided by sqrt(mean over its first norm_dim
+// dimensions of its squares + norm_eps) when norm_dim > 0, and written back (keys also to the cache).  Value
+// heads are copied to the cache.  Everything between the read and the write is float.
+constexpr int RNS_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(RNS_WARPS * 32)
+rope_norm_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
+                       const float* __restrict__ inv_freq, float amplitude, int norm_dim, float norm_eps,
+                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                       const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pages,
+                       T* __restrict__ v_pages, int page_size, long page_stride) {
+    __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
+    __shared__ float head_s[RNS_WARPS][ATT_MAX_HD_ROPE];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rot / 2;
+    const bool turn = inv_freq != nullptr && half > 0;
+    if (turn) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            sin_s[i] = sn * amplitude;
+            cos_s[i] = cs * amplitude;
+        }
+    }
+    __syncthreads();
+    T* row0 = qkv + (long)t * row_stride;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (k_pages != nullptr && n_kv > 0) {
+        const int b = seq_of_token[t];
+        const int page = block_table[(long)b * bt_stride + pos / page_size];
+        const long off = (long)page * page_stride + (long)(pos % page_size) * hd;
+        kdst = k_pages + off;
+        vdst = v_pages + off;
+    }
+    const long kv_head_stride = (long)page_size * hd;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total_heads = n_heads + 2 * n_kv;
+    const int per = (total_heads + gridDim.y - 1) / gridDim.y;
+    const int h_lo = blockIdx.y * per, h_hi = min(total_heads, h_lo + per);
+    float* hs = head_s[warp];
+    for (int head = h_lo + warp; head < h_hi; head += RNS_WARPS) {
+        T* row = row0 + (long)head * hd;
+        if (head >= n_heads + n_kv) {
+            if (vdst) {
+                T* d = vdst + (long)(head - n_heads - n_kv) * kv_head_stride;
+                for (int i = lane; i < hd; i += 32) d[i] = row[i];
+            }
+            continue;
+        }
+        for (int i = lane; i < hd; i += 32) hs[i] = to_float(row[i]);
+        __syncwarp();
+        float ss = 0.f;
+        float vals[ATT_MAX_HD_ROPE / 32];
+#pragma unroll
+        for (int r = 0; r < ATT_MAX_HD_ROPE / 32; ++r) {
+            const int i = lane + 32 * r;
+            float v = 0.f;
+            if (i < hd) {
+                v = hs[i];
+                if (turn && i < half) v = v * cos_s[i] - hs[i + half] * sin_s[i];
+                else if (turn && i < rot) v = v * cos_s[i - half] + hs[i - half] * sin_s[i - half];
+                if (i < norm_dim) ss = fmaf(v, v, ss);
+            }
+            vals[r] = v;
+        }
+        float inv = 1.0f;
+        if (norm_dim > 0) {
+            ss = warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)norm_dim + norm_eps);
+        }
+        T* d = (kdst && head >= n_heads) ? kdst + (long)(head - n_heads) * kv_head_stride : nullptr;
+#pragma unroll
+        for (int r = 0; r < ATT_MAX_HD_ROPE / 32; ++r) {
+            const int i = lane + 32 * r;
+            if (i < hd) {
+                const T o = from_float<T>(vals[r] * inv);
+                row[i] = o;
+                if (d) d[i] = o;
+            }
+        }
+        __syncwarp();
+    }
+}
+
 // ------------------------------------------------------------ attention
 // The keys a token sees, [start, pos], are cut into parts of ATT_PART = 256 consecutive keys counted from
 // `start`.  Within a part warp w of a block takes the key blocks w and w + 4 of 32 keys: lane j scores key j of
@@ -232,7 +324,7 @@ __device__ __forceinline__ float fold_value(float o, float a, float op, float b)
 template <typename T, int VEC, int G, int NREG>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restrict__ out, int n_heads, int n_kv,
-                         int hd, float scale, int window, const int* __restrict__ positions,
+                         int hd, float scale, float softcap, int window, const int* __restrict__ positions,
                          const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int bt_stride,
                          const T* __restrict__ k_pages, const T* __restrict__ v_pages, int page_size,
                          long page_stride, float* __restrict__ part_ml, float* __restrict__ part_o, int max_parts) {
@@ -304,7 +396,9 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
             float pr[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                const float sv = valid ? sc[g] * scale : -INFINITY;
+                float sv = sc[g] * scale;
+                if (softcap > 0.f) sv = softcap * tanhf(sv / softcap);       // a soft cap: scores stay inside (-cap, cap)
+                if (!valid) sv = -INFINITY;
                 const float m_new = fmaxf(m[g], warp_max(sv));   // lane 0 of the block is always valid
                 const float corr = expf(m[g] - m_new);           // exp(-inf) = 0 on the first block
                 pr[g] = valid ? expf(sv - m_new) : 0.f;
@@ -420,13 +514,13 @@ attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, cons
 
 template <typename T, int VEC, int G>
 static int launch_attention(const void* q, long q_row_stride, void* out, int T_, int n_heads, int n_kv, int hd, float scale,
-                            int window, const int* positions, const int* seq_of_token, const int* block_table,
+                            float softcap, int window, const int* positions, const int* seq_of_token, const int* block_table,
                             int bt_stride, const void* k_pages, const void* v_pages, int page_size, long page_stride,
                             float* part_ml, float* part_o, int max_parts, cudaStream_t stream) {
     dim3 grid(T_, n_heads / G, part_o ? max_parts : 1);
 #define ZLM_ATT_GO(NREG)                                                                                              \
     attention_general_kernel<T, VEC, G, NREG><<<grid, ATT_WARPS * 32, 0, stream>>>(                                     \
-        (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token, block_table,     \
+        (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, softcap, window, positions, seq_of_token, block_table, \
         bt_stride, (const T*)k_pages, (const T*)v_pages, page_size, page_stride, part_ml, part_o, max_parts)
     if (hd <= 128) ZLM_ATT_GO(4);
     else if (hd <= 256) ZLM_ATT_GO(8);
@@ -441,11 +535,11 @@ static int launch_attention(const void* q, long q_row_stride, void* out, int T_,
 
 template <typename T, int VEC>
 static int pick_group(int group, const void* q, long q_row_stride, void* out, int T_, int n_heads, int n_kv, int hd,
-                      float scale, int window, const int* positions, const int* seq_of_token, const int* block_table,
+                      float scale, float softcap, int window, const int* positions, const int* seq_of_token, const int* block_table,
                       int bt_stride, const void* k_pages, const void* v_pages, int page_size, long page_stride,
                       float* part_ml, float* part_o, int max_parts, cudaStream_t stream) {
 #define ZLM_ATT(GV)                                                                                                     \
-    launch_attention<T, VEC, GV>(q, q_row_stride, out, T_, n_heads, n_kv, hd, scale, window, positions, seq_of_token,   \
+    launch_attention<T, VEC, GV>(q, q_row_stride, out, T_, n_heads, n_kv, hd, scale, softcap, window, positions, seq_of_token, \
                                  block_table, bt_stride, k_pages, v_pages, page_size, page_stride, part_ml, part_o,     \
                                  max_parts, stream)
     if (group % 4 == 0 && hd <= 256) return ZLM_ATT(4);
@@ -499,6 +593,39 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
+// Like zlm_rope_store for rows [q heads | k heads | v heads | anything else] (row_stride elements a row), with the
+// cosines and sines multiplied by `amplitude` and, when norm_dim > 0, every rotated q and k head divided by the
+// root of (the mean of the squares of its first norm_dim dimensions + norm_eps) before it is written back and
+// stored.  inv_freq == nullptr: no rotation.  k_pages == nullptr: nothing is stored.
+ZLM_EXPORT int zlm_rope_norm_store(void* qkv, int dtype, long row_stride, int T, int n_heads, int n_kv, int hd, int rot,
+                                   const float* inv_freq, float amplitude, int norm_dim, float norm_eps,
+                                   const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
+                                   void* k_pages, void* v_pages, int page_size, long page_stride, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || rot < 0 || rot > hd || (rot & 1) || n_heads <= 0 || n_kv < 0 || page_size <= 0 || norm_dim < 0 ||
+        norm_dim > hd || (k_pages != nullptr && v_pages == nullptr))
+        return ZLM_ERR_BAD_ARG;
+    if (rot / 2 > ROPE_MAX_HALF || hd > ATT_MAX_HD_ROPE) return ZLM_ERR_UNSUPPORTED;
+    const int total_heads = n_heads + 2 * n_kv;
+    int parts = (296 + T - 1) / T;
+    if (parts > (total_heads + RNS_WARPS - 1) / RNS_WARPS) parts = (total_heads + RNS_WARPS - 1) / RNS_WARPS;
+    if (parts < 1) parts = 1;
+    dim3 grid(T, parts);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(rope_norm_store_kernel<float>, grid, dim3(RNS_WARPS * 32), 0, stream, (float*)qkv, row_stride,
+                       n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions, seq_of_token,
+                       block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size, page_stride);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(rope_norm_store_kernel<__nv_bfloat16>, grid, dim3(RNS_WARPS * 32), 0, stream, (__nv_bfloat16*)qkv,
+                       row_stride, n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions,
+                       seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size,
+                       page_stride);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
 // Floats of scratch memory that let zlm_attention_general spread a step of T tokens whose longest visible range
 // is max_keys keys over more blocks (0: the step has enough tokens, or one part of keys).
 ZLM_EXPORT long zlm_attention_general_scratch(int T, int n_heads, int n_kv, int hd, int max_keys) {
@@ -513,7 +640,7 @@ ZLM_EXPORT long zlm_attention_general_scratch(int T, int n_heads, int n_kv, int 
 // when it holds at least zlm_attention_general_scratch(...) floats and that is not 0, the parts of the keys are
 // computed by blocks of their own and folded by a second kernel; the result is bit for bit the same.
 ZLM_EXPORT int zlm_attention_general(const void* q, long q_row_stride, void* out, int dtype, int T, int n_heads,
-                                     int n_kv, int hd, float scale, int window, const int* positions,
+                                     int n_kv, int hd, float scale, float softcap, int window, const int* positions,
                                      const int* seq_of_token, const int* block_table, int bt_stride,
                                      const void* k_pages, const void* v_pages, int page_size, long page_stride,
                                      int max_keys, float* scratch, long scratch_floats, cudaStream_t stream) {
@@ -531,11 +658,11 @@ ZLM_EXPORT int zlm_attention_general(const void* q, long q_row_stride, void* out
     }
     const int group = n_heads / n_kv;
     if (dtype == ZLM_F32)
-        return pick_group<float, 4>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, window, positions,
+        return pick_group<float, 4>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, softcap, window, positions,
                                     seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size, page_stride,
                                     part_ml, part_o, max_parts, stream);
     if (dtype == ZLM_BF16)
-        return pick_group<__nv_bfloat16, 8>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, window, positions,
+        return pick_group<__nv_bfloat16, 8>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, softcap, window, positions,
                                             seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size,
                                             page_stride, part_ml, part_o, max_parts, stream);
     return ZLM_ERR_UNSUPPORTED;

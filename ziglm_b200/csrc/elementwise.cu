@@ -261,6 +261,56 @@ __global__ void norm_add_norm_kernel(const float* __restrict__ branch, const TW*
 }
 
 // x[t, :] += table[row, :] for every row t of x (a learned vector added to the whole step)
+// The norm behind a sublayer of an arrangement without norms before its sublayers, the residual sum with a
+// multiplier, and the rows the next sublayer reads (the new residual in the step's storage type):
+//   x[r] += mult * branch[r] / rms(branch[r]) * (w + off);   h[r] = x[r]      (h may be null)
+template <typename TW, typename TO>
+__global__ void norm_add_scaled_kernel(const float* __restrict__ branch, const TW* __restrict__ w, float off, float eps,
+                                       float mult, float* __restrict__ x, TO* __restrict__ h, int d) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* br = branch + (long)blockIdx.x * d;
+    float* xr = x + (long)blockIdx.x * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = br[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i] + mult * ((br[i] * inv) * (to_float(w[i]) + off));
+        xr[i] = v;
+        if (h != nullptr) h[(long)blockIdx.x * d + i] = from_float<TO>(v);
+    }
+}
+
+// out[i] = act(x[i]); kind 0: the squared relu, max(x, 0)^2
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ out, long n, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = fmaxf(to_float(x[i]), 0.f);
+    out[i] = from_float<T>(v * v);
+}
+
+// out[t, i] = a[t, i] * sigmoid(g[t, i]) over rows with strides of their own (a gate on the heads' outputs)
+template <typename T>
+__global__ void sigmoid_mul_kernel(const T* __restrict__ a, long a_stride, const T* __restrict__ g, long g_stride,
+                                   T* __restrict__ out, long out_stride, long total, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long t = idx / n;
+    const int i = (int)(idx - t * n);
+    const float gv = to_float(g[t * g_stride + i]);
+    out[t * out_stride + i] = from_float<T>(to_float(a[t * a_stride + i]) * (1.0f / (1.0f + expf(-gv))));
+}
+
 template <typename TW>
 __global__ void add_row_kernel(float* __restrict__ x, const TW* __restrict__ table_row, long total, int d) {
     pdl_launch_dependents();
@@ -484,6 +534,60 @@ ZLM_EXPORT int zlm_norm_add_norm(const float* branch, const void* w1, float off1
     else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_BF16) ZLM_NAN(__nv_bfloat16, __nv_bfloat16);
     else return ZLM_ERR_UNSUPPORTED;
 #undef ZLM_NAN
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// x rows (float, contiguous) += mult * RMS norm of branch rows (float, contiguous) with gain w + off; h (may be
+// null): the new rows of x in h_dtype.
+ZLM_EXPORT int zlm_norm_add_scaled(const float* branch, const void* w, int w_dtype, float off, float eps, float mult,
+                                   float* x, void* h, int h_dtype, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) return ZLM_ERR_BAD_ARG;
+    const int threads = norm_threads(d);
+    cudaError_t e;
+#define ZLM_NAS(TW, TO)                                                                                              \
+    e = launch_pdl(norm_add_scaled_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, branch, (const TW*)w, off, \
+                   eps, mult, x, (TO*)h, d)
+    if (w_dtype == ZLM_F32 && (h == nullptr || h_dtype == ZLM_F32)) ZLM_NAS(float, float);
+    else if (w_dtype == ZLM_F32 && h_dtype == ZLM_BF16) ZLM_NAS(float, __nv_bfloat16);
+    else if (w_dtype == ZLM_BF16 && (h == nullptr || h_dtype == ZLM_F32)) ZLM_NAS(__nv_bfloat16, float);
+    else if (w_dtype == ZLM_BF16 && h_dtype == ZLM_BF16) ZLM_NAS(__nv_bfloat16, __nv_bfloat16);
+    else return ZLM_ERR_UNSUPPORTED;
+#undef ZLM_NAS
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// kind 0: the squared relu.  out may be x.
+ZLM_EXPORT int zlm_unary_act(const void* x, void* out, int dtype, long n, int kind, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (kind != 0) return ZLM_ERR_BAD_ARG;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, n, kind);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(unary_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x,
+                       (__nv_bfloat16*)out, n, kind);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// out[t, i] = a[t, i] * sigmoid(g[t, i]), T rows of n elements, every operand with its own row stride.
+ZLM_EXPORT int zlm_sigmoid_mul(const void* a, long a_stride, const void* g, long g_stride, void* out, long out_stride,
+                               int dtype, int T, int n, cudaStream_t stream) {
+    if (T <= 0 || n <= 0) return 0;
+    const long total = (long)T * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(sigmoid_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)a, a_stride,
+                       (const float*)g, g_stride, (float*)out, out_stride, total, n);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(sigmoid_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a,
+                       a_stride, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, total, n);
+    else
+        return ZLM_ERR_UNSUPPORTED;
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 

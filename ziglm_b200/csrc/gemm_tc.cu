@@ -59,6 +59,7 @@ struct TcArgs {
     int glu_kind;        // gated mode: 0 silu, 1 tanh gelu
     float glu_limit;     // gated mode, silu: > 0 makes it the clamped swish min(g, L) sigmoid(slope min(g, L)) (clamp(u, -L, L) + 1)
     float glu_slope;
+    int unary_act;       // plain bf16 output: 0 none, 1 the squared relu max(y, 0)^2 on every element before it is rounded
     // RMSNorm split over two products (steps of a few tokens, see zlm_gemm_tc_norm):
     // this product finishes the residual sum and leaves x * gain as bf16 and the sums of squares per tile row
     const void* norm_gain;      // [N] gain of the norm that follows, or null
@@ -180,6 +181,7 @@ __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* t
             float val = __uint_as_float(v[j]);
             if (a.scale_ssq != nullptr) val *= inv_s[(c * 16 + j) & 63];
             val += bias_v;
+            if (!GLU && a.unary_act == 1) { val = fmaxf(val, 0.f); val *= val; }
             if (GLU) {
                 // even lanes hold a gate row, the next lane the matching up row
                 const float up = __shfl_down_sync(0xffffffffu, val, 1);
@@ -434,6 +436,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     for (int r = 1; r < 8; ++r) val += part[r];
                     if (a.scale_ssq != nullptr) val *= inv_s[cc];
                     val += bias_v;
+                    if (!GLU && a.unary_act == 1) { val = fmaxf(val, 0.f); val *= val; }
                     if (GLU) {
                         const float up = __shfl_down_sync(0xffffffffu, val, 1);
                         const float g = val;
@@ -492,6 +495,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         for (int r = 1; r < 8; ++r) v += part[u][r];     // in rank order
                         if (a.scale_ssq != nullptr) v *= inv_s[cc & 63];
                         v += bias_v;
+                        if (!GLU && a.unary_act == 1) { v = fmaxf(v, 0.f); v *= v; }
                         if (GLU) {
                             const float up = __shfl_down_sync(0xffffffffu, v, 1);
                             const float g = v;
@@ -993,7 +997,7 @@ static int gemm_tc_run(const void* X, const void* W, const void* bias, int bias_
                        int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
                        const void* norm_gain, int norm_gain_dtype, float norm_offset, void* norm_hb,
                        long ld_hb, float* norm_ssq, int* norm_fused, const float* scale_ssq, int scale_p,
-                       float scale_eps, float glu_limit, float glu_slope, cudaStream_t stream) {
+                       float scale_eps, float glu_limit, float glu_slope, cudaStream_t stream, int unary = 0) {
     if (norm_fused) *norm_fused = 0;
     if (T <= 0 || N <= 0) return 0;
     if (scale_ssq != nullptr && (T > 64 || scale_p <= 0)) return ZLM_ERR_BAD_ARG;
@@ -1015,6 +1019,7 @@ static int gemm_tc_run(const void* X, const void* W, const void* bias, int bias_
     a.glu_kind = glu == 2 ? 1 : 0;
     a.glu_limit = glu == 1 ? glu_limit : 0.f;
     a.glu_slope = glu_slope;
+    a.unary_act = (glu == 0 && !accumulate && y_dtype == ZLM_BF16) ? unary : 0;
     a.ksplit = 1;
     a.err = error_word();
     a.norm_gain = nullptr; a.norm_gain_dtype = norm_gain_dtype; a.norm_offset = norm_offset;
@@ -1110,6 +1115,14 @@ ZLM_EXPORT int zlm_gemm_tc_swish_clamped(const void* X, const void* W, const voi
                        nullptr, nullptr, nullptr, 0, 0.f, limit, slope, stream);
 }
 
+// Y = act(X W^T + bias) as bf16; unary 1: the squared relu.
+ZLM_EXPORT int zlm_gemm_tc_unary(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int T, int N,
+                                 int K, long ldx, long ldw, long ldy, int unary, cudaStream_t stream) {
+    if (unary != 1) return ZLM_ERR_BAD_ARG;
+    return gemm_tc_run(X, W, bias, bias_dtype, Y, ZLM_BF16, 0, 0, T, N, K, ldx, ldw, ldy, 0, nullptr, ZLM_F32, 0.f, nullptr, 0,
+                       nullptr, nullptr, nullptr, 0, 0.f, 0.f, 1.f, stream, unary);
+}
+
 ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
                            int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
                            cudaStream_t stream) {
@@ -1126,7 +1139,7 @@ constexpr int GROUP_STREAMS = 8;
 
 ZLM_EXPORT int zlm_gemm_tc_groups(const void* X, const void* W, void* Y, int y_dtype, int glu, const int* host_offs,
                                   int n_groups, int N, int K, long ldx, long ldw, long ldy, long w_group_stride,
-                                  int* launched, cudaStream_t stream) {
+                                  float glu_limit, float glu_slope, int* launched, cudaStream_t stream) {
     static cudaStream_t side[GROUP_STREAMS];
     static cudaEvent_t forked, joined[GROUP_STREAMS];
     static bool made = false;
@@ -1153,9 +1166,11 @@ ZLM_EXPORT int zlm_gemm_tc_groups(const void* X, const void* W, void* Y, int y_d
     for (int g = 0; g < n_groups && rc == 0; ++g) {
         const int rows = host_offs[g + 1] - host_offs[g];
         if (rows <= 0) continue;
-        rc = zlm_gemm_tc((const __nv_bfloat16*)X + (long)host_offs[g] * ldx,
+        // glu_limit > 0 (silu only): the clamped swish with that limit and slope
+        rc = gemm_tc_run((const __nv_bfloat16*)X + (long)host_offs[g] * ldx,
                          (const __nv_bfloat16*)W + (long)g * w_group_stride, nullptr, ZLM_F32,
                          (char*)Y + (size_t)host_offs[g] * ldy * y_el, y_dtype, 0, glu, rows, N, K, ldx, ldw, ldy, 0,
+                         nullptr, ZLM_F32, 0.f, nullptr, 0, nullptr, nullptr, nullptr, 0, 0.f, glu_limit, glu_slope,
                          lanes > 1 ? side[n % lanes] : stream);
         ++n;
     }

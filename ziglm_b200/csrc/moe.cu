@@ -3,6 +3,8 @@
 //
 // Routing, per token, in float:
 //   score_e  = sigmoid(z_e) or z_e's softmax                              (z: router logits)
+//   (or, mode 2: the experts with the largest logits are chosen and weighted by the softmax over the chosen
+//   logits alone)
 //   choice_e = score_e + correction_e                                     (correction may be absent)
 //   experts form n_groups equal groups of neighbours; a group's score is the sum of its group_best largest
 //   choice scores; only experts of the keep_groups best groups can be chosen (the others count as -inf);
@@ -19,6 +21,17 @@
 namespace zlm {
 
 constexpr int GM = 32, GN = 64, GK = 32;
+
+// act(gate) * up of an expert: silu(g) u, or with a limit L > 0 the clamped swish
+// min(g, L) sigmoid(slope min(g, L)) (clamp(u, -L, L) + 1)
+__device__ __forceinline__ float expert_glu(float g, float u, float limit, float slope) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        return (g / (1.0f + expf(-slope * g))) * u;
+    }
+    return (g / (1.0f + expf(-g))) * u;
+}
 
 // ------------------------------------------------------------------- routing
 // one block of RT_WARPS warps per token; shared: score[E], choice[E], group score[n_groups], and the token's
@@ -69,14 +82,16 @@ route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_strid
     if (warp != 0) return;
     const float* zr = logit;
     float zmax = -INFINITY, zsum = 0.f;
-    if (softmax_scores) {
+    if (softmax_scores == 1) {
         for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, zr[e]);
         zmax = warp_max(zmax);
         for (int e = lane; e < E; e += 32) zsum += expf(zr[e] - zmax);
         zsum = warp_sum(zsum);
     }
     for (int e = lane; e < E; e += 32) {
-        const float s = softmax_scores ? expf(zr[e] - zmax) / zsum : 1.0f / (1.0f + expf(-zr[e]));
+        // 2: the logit itself is the choice score; the weights are the softmax over the chosen logits (below)
+        const float s = softmax_scores == 2 ? zr[e]
+                        : (softmax_scores ? expf(zr[e] - zmax) / zsum : 1.0f / (1.0f + expf(-zr[e])));
         score[e] = s;
         choice[e] = correction ? s + correction[e] : s;
     }
@@ -132,6 +147,20 @@ route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_strid
         }
         wsum += score[best_e];
         __syncwarp();
+    }
+    if (softmax_scores == 2) {
+        if (lane == 0) {
+            // the first chosen logit is the largest
+            const float first = weights[(long)t * top];
+            float total = 0.f;
+            for (int k = 0; k < top; ++k) {
+                const float w = expf(weights[(long)t * top + k] - first);
+                weights[(long)t * top + k] = w;
+                total += w;
+            }
+            for (int k = 0; k < top; ++k) weights[(long)t * top + k] /= total;
+        }
+        return;
     }
     if (renormalize && lane == 0)
         for (int k = 0; k < top; ++k) weights[(long)t * top + k] /= wsum;
@@ -198,8 +227,9 @@ __global__ void group_kernel(const int* __restrict__ ids, int P, int E, int* __r
 template <typename TX, typename TW, bool GLU>
 __global__ void __launch_bounds__(256)
 grouped_kernel(const TX* __restrict__ x, long x_stride, const TW* __restrict__ w, void* __restrict__ out_, long out_stride,
-               int N, int K, int top, int interleaved, const int* __restrict__ offs, const int* __restrict__ sorted,
-               const int* __restrict__ tile_expert, const int* __restrict__ tile_row, const int* __restrict__ n_tiles) {
+               int N, int K, int top, int interleaved, float glu_limit, float glu_slope, const int* __restrict__ offs,
+               const int* __restrict__ sorted, const int* __restrict__ tile_expert, const int* __restrict__ tile_row,
+               const int* __restrict__ n_tiles) {
     __shared__ float xs[GK][GM + 1];
     __shared__ float ws[GLU ? 2 : 1][GK][GN + 1];
     __shared__ int row_in[GM], row_out[GM];
@@ -259,7 +289,7 @@ grouped_kernel(const TX* __restrict__ x, long x_stride, const TW* __restrict__ w
             if (n >= N) continue;
             if (GLU) {
                 const float g = round_to<TX>(acc[0][r][j]), u = round_to<TX>(acc[GLU ? 1 : 0][r][j]);
-                ((TX*)out_)[(long)row_out[lr] * out_stride + n] = from_float<TX>((g / (1.0f + expf(-g))) * u);
+                ((TX*)out_)[(long)row_out[lr] * out_stride + n] = from_float<TX>(expert_glu(g, u, glu_limit, glu_slope));
             } else {
                 ((float*)out_)[(long)row_out[lr] * out_stride + n] = acc[0][r][j];
             }
@@ -294,8 +324,8 @@ template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfl
 template <typename TX, bool GLU>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 grouped_skinny_kernel(const TX* __restrict__ x, long x_stride, const TX* __restrict__ w, void* __restrict__ out_,
-                      long out_stride, int N, int K, int top, int interleaved, const int* __restrict__ offs,
-                      const int* __restrict__ sorted, const int* __restrict__ tile_expert,
+                      long out_stride, int N, int K, int top, int interleaved, float glu_limit, float glu_slope,
+                      const int* __restrict__ offs, const int* __restrict__ sorted, const int* __restrict__ tile_expert,
                       const int* __restrict__ tile_row, const int* __restrict__ n_tiles) {
     extern __shared__ __align__(16) unsigned char sk_raw[];
     TX* xs = reinterpret_cast<TX*>(sk_raw);                     // [SK_ROWS][K]
@@ -353,7 +383,7 @@ grouped_skinny_kernel(const TX* __restrict__ x, long x_stride, const TX* __restr
                 if (lane == 0 && r < rows) {
                     if (GLU) {
                         const float gr = round_to<TX>(g), ur = round_to<TX>(u);
-                        ((TX*)out_)[(long)row_out[r] * out_stride + n] = from_float<TX>((gr / (1.0f + expf(-gr))) * ur);
+                        ((TX*)out_)[(long)row_out[r] * out_stride + n] = from_float<TX>(expert_glu(gr, ur, glu_limit, glu_slope));
                     } else {
                         ((float*)out_)[(long)row_out[r] * out_stride + n] = g;
                     }
@@ -443,7 +473,7 @@ ZLM_EXPORT int zlm_moe_group(const int* ids, int P, int E, int* offs, int* sorte
 // skinny: the step has few tokens; an expert's weights are streamed once against up to 8 rows at a time.
 ZLM_EXPORT int zlm_moe_grouped(const void* x, int x_dtype, long x_stride, const void* w, int w_dtype, void* out,
                                long out_stride, int glu, int interleaved, int skinny, int P, int E, int N, int K, int top,
-                               const int* offs, const int* sorted, const int* tile_expert, const int* tile_row,
+                               float glu_limit, float glu_slope, const int* offs, const int* sorted, const int* tile_expert, const int* tile_row,
                                const int* n_tiles, cudaStream_t stream) {
     if (P <= 0) return 0;
     if (E <= 0 || N <= 0 || K <= 0 || top <= 0) return ZLM_ERR_BAD_ARG;
@@ -465,7 +495,8 @@ ZLM_EXPORT int zlm_moe_grouped(const void* x, int x_dtype, long x_stride, const 
             allowed = 160 * 1024;                                                                                    \
         }                                                                                                            \
         e = launch_pdl(grouped_skinny_kernel<TX, GLU>, sgrid, dim3(SK_WARPS * 32), sk_smem, stream, (const TX*)x, x_stride, \
-                       (const TX*)w, out, out_stride, N, K, top, interleaved, offs, sorted, tile_expert, tile_row, n_tiles); \
+                       (const TX*)w, out, out_stride, N, K, top, interleaved, glu_limit, glu_slope, offs, sorted, tile_expert,  \
+                       tile_row, n_tiles);                                                                           \
     } while (0)
         if (x_dtype == ZLM_F32) { if (glu) ZLM_SK(float, true); else ZLM_SK(float, false); }
         else { if (glu) ZLM_SK(__nv_bfloat16, true); else ZLM_SK(__nv_bfloat16, false); }
@@ -475,7 +506,7 @@ ZLM_EXPORT int zlm_moe_grouped(const void* x, int x_dtype, long x_stride, const 
     dim3 grid((N + GN - 1) / GN, (unsigned)max_tiles);
 #define ZLM_GR(TX, TW, GLU)                                                                                         \
     e = launch_pdl(grouped_kernel<TX, TW, GLU>, grid, dim3(256), 0, stream, (const TX*)x, x_stride, (const TW*)w, out, \
-                   out_stride, N, K, top, interleaved, offs, sorted, tile_expert, tile_row, n_tiles)
+                   out_stride, N, K, top, interleaved, glu_limit, glu_slope, offs, sorted, tile_expert, tile_row, n_tiles)
     if (x_dtype == ZLM_F32 && w_dtype == ZLM_F32) { if (glu) ZLM_GR(float, float, true); else ZLM_GR(float, float, false); }
     else if (x_dtype == ZLM_BF16 && w_dtype == ZLM_BF16) { if (glu) ZLM_GR(__nv_bfloat16, __nv_bfloat16, true); else ZLM_GR(__nv_bfloat16, __nv_bfloat16, false); }
     else return ZLM_ERR_UNSUPPORTED;

@@ -57,6 +57,10 @@ _PROTOTYPES = {
                                 c_float, c_void_p],
         "zlm_norm_add_norm": [c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p,
                               c_int, c_int, c_int, c_void_p],
+        "zlm_norm_add_scaled": [c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+                                c_void_p],
+        "zlm_unary_act": [c_void_p, c_void_p, c_int, c_long, c_int, c_void_p],
+        "zlm_sigmoid_mul": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
         "zlm_add_row": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "zlm_scale": [c_void_p, c_long, c_float, c_void_p],
         "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
@@ -79,7 +83,8 @@ _PROTOTYPES = {
         "zlm_moe_max_tiles_scratch": [c_int, c_int],
         "zlm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "zlm_moe_grouped": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
-                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                            c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p],
         "zlm_moe_gather": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "zlm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
@@ -90,7 +95,9 @@ _PROTOTYPES = {
     "attention": {
         "zlm_rope_store": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
-        "zlm_attention_general": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+        "zlm_rope_norm_store": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_int,
+                                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
+        "zlm_attention_general": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_int,
                                   c_void_p, c_long, c_void_p],
         "zlm_attention_general_scratch": [c_int, c_int, c_int, c_int, c_int],
@@ -122,10 +129,12 @@ _PROTOTYPES = {
         "zlm_gemm_tc_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_long, c_long, c_long, c_int, c_void_p, c_int, c_float, c_void_p, c_long, c_void_p,
                              c_void_p, c_void_p, c_int, c_float, c_void_p],
+        "zlm_gemm_tc_unary": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
+                              c_int, c_void_p],
         "zlm_gemm_tc_swish_clamped": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_long, c_long,
                                       c_long, c_float, c_float, c_void_p],
         "zlm_gemm_tc_groups": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_long, c_long,
-                               c_long, c_long, c_void_p, c_void_p],
+                               c_long, c_long, c_float, c_float, c_void_p, c_void_p],
         "zlm_gemm_tc_status": [c_void_p],
         "zlm_gemm_tc_wait_selftest": [c_int, c_void_p, c_void_p],
     },
@@ -290,6 +299,47 @@ def norm_add_norm(branch: torch.Tensor, w1: torch.Tensor, eps1: float, x: torch.
     return True
 
 
+def norm_add_scaled(branch: torch.Tensor, weight: torch.Tensor, eps: float, mult: float, x: torch.Tensor,
+                    h: Optional[torch.Tensor] = None, weight_offset: float = 0.0) -> None:
+    """x += mult * branch / sqrt(mean(branch^2) + eps) * (weight + weight_offset), row by row, and with ``h`` also
+    h = x (the new rows, in h's type): the norm behind a sublayer whose input is the residual stream itself.
+    branch and x float32 [n, d] contiguous."""
+    _cuda(branch, "branch", torch.float32); _cuda(x, "x", torch.float32); _cuda(weight, "weight")
+    n, d = x.shape
+    if branch.shape != (n, d) or weight.numel() != d:
+        raise KernelError("norm_add_scaled: shapes do not match")
+    if h is not None:
+        _cuda(h, "h")
+        if h.shape != (n, d):
+            raise KernelError("norm_add_scaled: h must have the shape of x")
+    _check(_fn("elementwise", "zlm_norm_add_scaled")(
+        branch.data_ptr(), weight.data_ptr(), code(weight.dtype), float(weight_offset), float(eps), float(mult),
+        x.data_ptr(), _ptr(h), code(h.dtype) if h is not None else F32, n, d, _stream()), "norm_add_scaled")
+
+
+UNARY_ACTIVATIONS = {"relu2": 0}
+
+
+def unary_act(x: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(x) element by element (out may be x); "relu2": max(x, 0)^2."""
+    _cuda(x, "x"); _cuda(out, "out", x.dtype)
+    if activation not in UNARY_ACTIVATIONS or out.shape != x.shape:
+        raise KernelError(f"unary_act: activation {activation!r} is not known, or the shapes differ")
+    _check(_fn("elementwise", "zlm_unary_act")(x.data_ptr(), out.data_ptr(), code(x.dtype), x.numel(),
+                                               UNARY_ACTIVATIONS[activation], _stream()), "unary_act")
+
+
+def sigmoid_mul(a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a * sigmoid(gate); all [T, n] of one type, each may be a column slice of a wider matrix."""
+    _rows(a, "a"); _rows(gate, "gate"); _rows(out, "out")
+    if a.shape != gate.shape or a.shape != out.shape or a.dtype != gate.dtype or a.dtype != out.dtype:
+        raise KernelError("sigmoid_mul: shapes or types do not match")
+    T, n = a.shape
+    _check(_fn("elementwise", "zlm_sigmoid_mul")(a.data_ptr(), _row_stride(a), gate.data_ptr(), _row_stride(gate),
+                                                 out.data_ptr(), _row_stride(out), code(a.dtype), T, n, _stream()),
+           "sigmoid_mul")
+
+
 def add_row(x: torch.Tensor, row: torch.Tensor) -> None:
     """x[t, :] += row for every t; x is float32 [T, d], row holds d elements."""
     _cuda(x, "x", torch.float32); _cuda(row, "row")
@@ -379,13 +429,14 @@ def gated_scan(u: torch.Tensor, gates: torch.Tensor, gate_block: int, y: torch.T
 
 # ------------------------------------------------------------ mixture of experts
 def moe_route(z: Optional[torch.Tensor], correction: Optional[torch.Tensor], top: int, n_groups: int, keep_groups: int,
-              group_best: int, ids: torch.Tensor, weights: torch.Tensor, softmax_scores: bool = False,
+              group_best: int, ids: torch.Tensor, weights: torch.Tensor, softmax_scores=False,
               renormalize: bool = False, h: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None) -> None:
     """Per token: scores = sigmoid(z) (or softmax), chosen by score + correction within the ``keep_groups`` groups
     whose ``group_best`` best choice scores sum highest; ids int32 [T, top], weights float32 [T, top] (the scores
     of the chosen, divided by their sum with ``renormalize``).  ``z``: float32 [T, E] router logits; or None with
     ``h`` [T, d] and ``router`` [E, d] of one type: the logits are then taken inside (float32 sums), which is what
-    a step of few tokens wants."""
+    a step of few tokens wants.  ``softmax_scores`` = 2: the experts with the largest logits are chosen and their
+    weights are the softmax over the chosen logits alone (no correction, no groups)."""
     _cuda(ids, "ids", torch.int32); _cuda(weights, "weights", torch.float32)
     d, h_stride, h_code = 0, 0, F32
     if z is not None:
@@ -435,11 +486,13 @@ def moe_group(ids: torch.Tensor, n_experts: int, offs: torch.Tensor, order: torc
 
 def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, glu: bool, n_pairs: int, top: int,
                 offs: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor, tile_row: torch.Tensor,
-                n_tiles: torch.Tensor, interleaved: bool = False, skinny: bool = False) -> None:
+                n_tiles: torch.Tensor, interleaved: bool = False, skinny: bool = False, limit: float = 0.0,
+                slope: float = 1.0) -> None:
     """The experts' products over the grouped pairs.  ``glu``: x [T, K] by token, w [E, 2N, K] (gate rows, then up
     rows; alternating with ``interleaved``), out [P, N] = silu(gate) * up in x's type, rows in grouped order.
     Otherwise: x [P, K] in grouped order, w [E, N, K], out float32 [P, N] with row p the result of pair p.
-    ``skinny``: the step has few tokens, so an expert's weights are streamed once against its few rows."""
+    ``skinny``: the step has few tokens, so an expert's weights are streamed once against its few rows.
+    ``limit`` > 0 (with ``glu``): out = g sigmoid(slope g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit)."""
     _rows(x, "x"); _cuda(w, "w"); _rows(out, "out")
     E, NW, K = w.shape
     N = NW // 2 if glu else NW
@@ -447,7 +500,8 @@ def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, glu: bool, 
         raise KernelError("moe_grouped: shapes or types do not match")
     _check(_fn("moe", "zlm_moe_grouped")(
         x.data_ptr(), code(x.dtype), _row_stride(x), w.data_ptr(), code(w.dtype), out.data_ptr(), _row_stride(out),
-        int(glu), int(interleaved), int(skinny), n_pairs, E, N, K, top, offs.data_ptr(), order.data_ptr(),
+        int(glu), int(interleaved), int(skinny), n_pairs, E, N, K, top, float(limit), float(slope), offs.data_ptr(),
+        order.data_ptr(),
         tile_expert.data_ptr(), tile_row.data_ptr(), n_tiles.data_ptr(), _stream()), "moe_grouped")
 
 
@@ -461,11 +515,13 @@ def moe_gather(x: torch.Tensor, order: torch.Tensor, top: int, rows: torch.Tenso
                                         rows.data_ptr(), P, d, _stream()), "moe_gather")
 
 
-def gemm_tc_groups(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, host_offs, glu: Optional[str] = None) -> bool:
+def gemm_tc_groups(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, host_offs, glu: Optional[str] = None,
+                   limit: float = 0.0, slope: float = 1.0) -> bool:
     """One tensor-core product per group of consecutive rows: rows host_offs[g]..host_offs[g+1] of x [P, K] meet
     w[g] ([G, N, K], bf16) and give the same rows of out ([P, N], or [P, N/2] bf16 with ``glu``, whose rows of
     w[g] alternate gate and up).  ``host_offs``: a C array of G + 1 ints on the host.  False, with nothing or only
-    some groups done, if the operands are not what TMA can read."""
+    some groups done, if the operands are not what TMA can read.  ``limit`` > 0 with ``glu`` "silu": the clamped
+    swish of ``gated_act`` with that limit and slope."""
     global _launches
     _cuda(x, "x", torch.bfloat16); _cuda(w, "w", torch.bfloat16); _cuda(out, "out")
     G, N, K = w.shape
@@ -475,7 +531,7 @@ def gemm_tc_groups(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, host_off
     launched = ctypes.c_int(0)
     status = _fn("gemm_tc", "zlm_gemm_tc_groups")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), code(out.dtype), GLU_KINDS[glu] if glu else 0, host_offs, G, N, K,
-        K, K, n_out, N * K, ctypes.byref(launched), _stream())
+        K, K, n_out, N * K, float(limit), float(slope), ctypes.byref(launched), _stream())
     _launches += launched.value
     if status == -2:
         return False
@@ -589,6 +645,36 @@ def rope_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary
         _ptr(k_pages), _ptr(v_pages), page_size, page_stride, _stream()), "rope_store")
 
 
+def rope_norm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary_dim: int,
+                    inv_freq: Optional[torch.Tensor], amplitude: float, norm_dim: int, norm_eps: float,
+                    positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], page_size: int) -> None:
+    """``rope_store`` with an amplitude on the cosines and sines and a unit RMS norm behind the rotation: every
+    q and k head of a row [q heads | k heads | v heads | ...] of qkv is turned, divided by
+    sqrt(mean of the squares of its first ``norm_dim`` dimensions + norm_eps) (``norm_dim`` 0: not divided), written
+    back and (keys, values) stored in the cache pages.  The row may be wider than the heads."""
+    _rows(qkv, "qkv"); _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] < (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("rope_norm_store: the rows are narrower than the heads")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() * 2 != rotary_dim:
+            raise KernelError("rope_norm_store: the frequency table must hold rotary_dim/2 entries")
+    page_stride = 0
+    if k_pages is not None:
+        _cuda(k_pages, "k_pages", qkv.dtype); _cuda(v_pages, "v_pages", qkv.dtype)
+        if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+            raise KernelError("rope_norm_store: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+        page_stride = k_pages.stride(0)
+    _check(_fn("attention", "zlm_rope_norm_store")(
+        qkv.data_ptr(), code(qkv.dtype), _row_stride(qkv), T, n_heads, n_kv, head_dim, rotary_dim, _ptr(inv_freq),
+        float(amplitude), int(norm_dim), float(norm_eps), positions.data_ptr(), seq_of_token.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), _ptr(k_pages), _ptr(v_pages), page_size, page_stride, _stream()),
+        "rope_norm_store")
+
+
 def attention_general_scratch(n_tokens: int, n_heads: int, n_kv: int, head_dim: int, max_keys: int) -> int:
     """Floats of scratch with which ``attention_general`` spreads a step of few tokens over more blocks (0: none
     is of use)."""
@@ -598,8 +684,10 @@ def attention_general_scratch(n_tokens: int, n_heads: int, n_kv: int, head_dim: 
 def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
                       window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                       block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
-                      page_size: int, max_keys: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
-    """out[t, h, :] = softmax(q[t,h] . K[start..pos_t] * scale) @ V over the paged cache.
+                      page_size: int, max_keys: int = 0, scratch: Optional[torch.Tensor] = None,
+                      softcap: float = 0.0) -> None:
+    """out[t, h, :] = softmax(q[t,h] . K[start..pos_t] * scale) @ V over the paged cache; with ``softcap`` c > 0 the
+    scaled scores become c * tanh(score / c) before the softmax.
 
     The queries are the first n_heads*head_dim columns of each row of ``qkv`` (any row stride).
     ``max_keys`` (the most keys a token of the step sees) and ``scratch`` (float32, at least
@@ -620,7 +708,7 @@ def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: 
         raise KernelError("attention: cache pages must be [n_pages, n_kv, page_size, head_dim]")
     _check(_fn("attention", "zlm_attention_general")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), code(qkv.dtype), T, n_heads, n_kv, head_dim, scale,
-        int(window or 0), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+        float(softcap or 0.0), int(window or 0), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), page_size, k_pages.stride(0), int(max_keys),
         _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream()),
         "attention_general")
@@ -842,9 +930,10 @@ def attention_with_rope(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int
 
 
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
-              window: Optional[int], io) -> None:
-    """Attention of a step's tokens over the cache of the running layer; picks the kernel."""
-    if _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
+              window: Optional[int], io, softcap: float = 0.0) -> None:
+    """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``softcap`` c > 0:
+    the scaled scores become c * tanh(score / c)."""
+    if not softcap and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
         if n_blocks > 0:
             need = attention_decode_flat_scratch(step.n_tokens, n_heads, n_kv, head_dim, n_blocks)
@@ -874,11 +963,13 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
     need = attention_general_scratch(step.n_tokens, n_heads, n_kv, head_dim, max_keys)
     scratch = step.ws.buf("attn_parts", (need,), torch.float32) if need > 0 else None
     attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
-                      io.block_table, io.k_pages, io.v_pages, io.page_size, max_keys, scratch)
+                      io.block_table, io.k_pages, io.v_pages, io.page_size, max_keys, scratch, softcap=softcap)
 
 
-def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1):
+def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1, softcap: float = 0.0):
     """The sources of the tensor-core attention kernels if they take this shape, else nothing (the plain kernel runs)."""
+    if softcap:
+        return ()
     return ("attention_tc", "attention_fmha") if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
 
 
@@ -977,6 +1068,32 @@ def gemm_tc_swish_clamped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, l
     if status == -2:
         return False
     _check(status, "gemm_tc_swish_clamped")
+    return True
+
+
+def gemm_tc_unary(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str,
+                  bias: Optional[torch.Tensor] = None) -> bool:
+    """out [T, N] (bf16) = act(x w^T + bias) on the tensor cores, the activation applied to the float32 sums in the
+    epilogue ("relu2": max(y, 0)^2).  False, having done nothing, if the operands are not what TMA can read."""
+    _rows(x, "x"); _rows(w, "w"); _rows(out, "out")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_unary: x, w and out must be bfloat16")
+    if activation != "relu2":
+        raise KernelError(f"gemm_tc_unary: activation {activation!r} is not known (relu2)")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (T, N):
+        raise KernelError("gemm_tc_unary: shapes do not match")
+    if bias is not None:
+        _cuda(bias, "bias")
+        if bias.numel() != N:
+            raise KernelError("gemm_tc_unary: bias length does not match")
+    status = _fn("gemm_tc", "zlm_gemm_tc_unary")(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), code(bias.dtype) if bias is not None else F32, out.data_ptr(), T, N, K,
+        _row_stride(x), _row_stride(w), _row_stride(out), 1, _stream())
+    if status == -2:
+        return False
+    _check(status, "gemm_tc_unary")
     return True
 
 

@@ -47,7 +47,7 @@ class ParamDecl:
     """A tensor a part owns: its shape, whether it is a table of integers, how random weights fill it."""
     shape: Tuple[int, ...]
     kind: str = "float"            # "float" or "int"
-    init: str = "normal"           # "normal" (N(0, std)) or "ones" (norm weights)
+    init: str = "normal"           # "normal" (N(0, std)), "ones" (norm weights) or "zeros" (norm weights kept minus one)
 
 
 @dataclass(frozen=True)

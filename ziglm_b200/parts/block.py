@@ -12,6 +12,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
+from .. import kernels
 from ..config.spec import LayerSpec
 from .base import (KVNeed, LayerIO, ParamDecl, Part, StateNeed, feed_forward_class, mixer_class, norm_class,
                    register_block)
@@ -183,3 +184,106 @@ class SandwichBlock(Part):
 
 
 register_block("sandwich", SandwichBlock)
+
+
+class PostNormBlock(Part):
+    """Norms behind the sublayers only, and a multiplier on what they add: x += m * post1(mixer(x)) and, where the
+    layer has a feed-forward, x += m * post2(ffn(x)).  The sublayers read the residual stream itself (its rows in
+    the step's storage type; in float32 the residual as it is).
+
+    The two post-norms come in ``LayerSpec.options`` (``mixer_post_norm``, ``ffn_post_norm``) and m as
+    ``residual_mult`` (default 1).  A sublayer writes its output into a float32 branch buffer; the post-norm reads
+    it in float32, adds the multiplied rows into the residual and leaves the new rows for the sublayer that follows,
+    here or in the next block, all in one kernel.  ``mixer_norm`` is the part that makes those rows when nobody has
+    (the first block of a model, or a block behind one of another arrangement)."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        self.mult = float(spec.options.get("residual_mult", 1.0))
+        self.mixer_norm = norm_class("cast")(None, dtype, device)
+        self.parts: Dict[str, Part] = {}
+        for prefix, klass, sub in self._children(spec):
+            self.parts[prefix] = klass(sub, dtype, device)
+        self.mixer = self.parts["mixer."]
+        self.mixer_post = self.parts["mixer_post_norm."]
+        self.ffn = self.parts.get("ffn.")
+        self.ffn_post = self.parts.get("ffn_post_norm.")
+
+    @classmethod
+    def _children(cls, spec: LayerSpec):
+        post = spec.options["mixer_post_norm"]
+        out = [("mixer.", mixer_class(spec.mixer.kind), spec.mixer),
+               ("mixer_post_norm.", norm_class(post.kind), post)]
+        if spec.ffn is not None:
+            post = spec.options["ffn_post_norm"]
+            out += [("ffn.", feed_forward_class(spec.ffn.kind), spec.ffn),
+                    ("ffn_post_norm.", norm_class(post.kind), post)]
+        return out
+
+    @classmethod
+    def declare(cls, spec: LayerSpec) -> Dict[str, ParamDecl]:
+        out: Dict[str, ParamDecl] = {}
+        for prefix, klass, sub in cls._children(spec):
+            for name, decl in klass.declare(sub).items():
+                out[prefix + name] = decl
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for prefix, part in self.parts.items():
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        libs: Tuple[str, ...] = self.mixer_norm.kernel_libraries()
+        for part in self.parts.values():
+            libs += part.kernel_libraries()
+        return libs
+
+    def cache_needs(self) -> Optional[KVNeed]:
+        return self.mixer.cache_needs()
+
+    def state_needs(self) -> Optional[StateNeed]:
+        return self.mixer.state_needs()
+
+    def accepts_normed_input(self) -> bool:
+        """The block before may hand over the rows this block's mixer reads (``h_in``)."""
+        return True
+
+    def _close(self, step, post, branch: torch.Tensor, x: torch.Tensor, want_rows: bool, name: str):
+        """x += m * post(branch); with ``want_rows`` also the new rows of x for the sublayer that follows."""
+        if hasattr(post, "add_scaled"):
+            if not want_rows or self.dtype == torch.float32:
+                post.add_scaled(step, branch, x, self.mult)
+                return x if want_rows else None
+            return post.add_scaled(step, branch, x, self.mult, rows_out=step.ws.buf(name, tuple(x.shape), self.dtype))
+        # a norm without the fused form: norm into the branch's own rows, multiply, add
+        normed = step.ws.buf("branch_normed", tuple(x.shape), torch.float32)
+        post.forward_rows(branch, normed)
+        if self.mult != 1.0:
+            kernels.scale_(normed, self.mult)
+        kernels.add_(x, normed)
+        return self.mixer_norm.forward(step, x, name=name) if want_rows else None
+
+    def forward(self, step, io: LayerIO, x: torch.Tensor, h_in=None, next_norm=None):
+        """``h_in``: the rows the mixer reads, left by the block before.  ``next_norm``: the first part of the block
+        after; if that block reads the residual itself (its part is the cast) the result is the rows it reads."""
+        h = h_in if isinstance(h_in, torch.Tensor) else self.mixer_norm.forward(step, x, name="rows_mixer")
+        feeds_next = type(next_norm) is type(self.mixer_norm)
+        branch = step.ws.buf("branch", tuple(x.shape), torch.float32)
+        if self.mixer.can_overwrite:
+            self.mixer.forward(step, io, h, branch, accumulate=False)
+        else:
+            branch.zero_()
+            self.mixer.forward(step, io, h, branch)
+        if self.ffn is None:
+            return self._close(step, self.mixer_post, branch, x, feeds_next, "rows_next")
+        h = self._close(step, self.mixer_post, branch, x, True, "rows_ffn")
+        branch = step.ws.buf("branch", tuple(x.shape), torch.float32)
+        if self.ffn.can_overwrite:
+            self.ffn.forward(step, h, branch, accumulate=False)
+        else:
+            branch.zero_()
+            self.ffn.forward(step, h, branch)
+        return self._close(step, self.ffn_post, branch, x, feeds_next, "rows_next")
+
+
+register_block("postnorm", PostNormBlock)

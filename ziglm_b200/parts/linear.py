@@ -47,6 +47,13 @@ class Linear:
         kernels.gemm_generic(x, self.weight, out, bias=self.bias, accumulate=accumulate)
         return out
 
+    def with_activation(self, x: torch.Tensor, out: torch.Tensor, activation: str) -> bool:
+        """out = act(x W^T + bias) in one kernel where the tensor-core product takes the operands; False, having
+        done nothing, where it does not (the caller runs the product and the activation kernel)."""
+        if x.dtype != torch.bfloat16 or self.weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            return False
+        return kernels.gemm_tc_unary(x, self.weight, out, activation, bias=self.bias)
+
     def accumulate_with_norm(self, step, x: torch.Tensor, residual: torch.Tensor, norm, name: str) -> Optional[NormedInput]:
         """residual += x W^T (+ bias); if the step is small enough for the product to finish every element of
         the residual in one thread, it also does the first half of ``norm`` (an RMSNorm part) and the result

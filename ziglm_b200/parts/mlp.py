@@ -102,3 +102,48 @@ class GatedMLP(Part):
 
 
 register_feed_forward("gated_mlp", GatedMLP)
+
+
+class PlainMLP(Part):
+    """A feed-forward without a gate: down(act(up(x))).  ``activation``: "relu2", the squared relu max(z, 0)^2."""
+    can_overwrite = True
+
+    def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        if spec.activation not in kernels.UNARY_ACTIVATIONS:
+            raise ValueError(f"mlp: activation {spec.activation!r} is not known ({', '.join(kernels.UNARY_ACTIVATIONS)})")
+        self.intermediate = spec.intermediate
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    @classmethod
+    def declare(cls, spec: FeedForwardSpec) -> Dict[str, ParamDecl]:
+        p = {"up.weight": ParamDecl((spec.intermediate, spec.width)),
+             "down.weight": ParamDecl((spec.width, spec.intermediate))}
+        if spec.bias:
+            p["up.bias"] = ParamDecl((spec.intermediate,))
+            p["down.bias"] = ParamDecl((spec.width,))
+        return p
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = Linear(tensors["up.weight"], tensors["up.bias"] if self.spec.bias else None)
+        self.down = Linear(tensors["down.weight"], tensors["down.bias"] if self.spec.bias else None)
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        libs = ("elementwise",)
+        for lin in (self.up, self.down):
+            if lin is not None:
+                libs += lin.libraries(self.dtype)
+        return libs
+
+    def forward(self, step, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True):
+        T = residual.shape[0]
+        act = step.ws.buf("ffn_act", (T, self.intermediate), self.dtype)
+        if not self.up.with_activation(h, act, self.spec.activation):
+            self.up(h, act)
+            kernels.unary_act(act, act, self.spec.activation)
+        self.down(act, residual, accumulate=accumulate)
+        return None
+
+
+register_feed_forward("mlp", PlainMLP)

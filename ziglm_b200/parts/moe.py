@@ -5,8 +5,12 @@
     best choice scores, and only experts of the ``keep_groups`` best groups can be chosen;
     out = sum over the chosen e of score_e * W_down[e] (act(W_gate[e] h) * (W_up[e] h))
 (the weights are divided by their sum only with ``renormalize``).  Options of the spec: ``experts``, ``top``,
-``groups``, ``keep_groups``, ``group_best``, ``score`` ("sigmoid" or "softmax"), ``correction`` (whether a
-learned offset per expert enters the choice), ``renormalize``.
+``groups``, ``keep_groups``, ``group_best``, ``score`` ("sigmoid", "softmax", or "softmax_chosen": the experts with
+the largest logits, weighted by the softmax over the chosen logits alone), ``correction`` (whether a learned offset
+per expert enters the choice), ``renormalize``.  The experts' activation is silu(gate) * up, or with
+``activation`` "swish_clamped" and the options ``limit`` and ``slope`` the clamped form
+min(g, L) sigmoid(slope min(g, L)) (clamp(u, -L, L) + 1).  ``shared``: the spec of a feed-forward that runs for
+every token and is added to the experts' sum (its tensors under ``shared.``).
 
 The (token, choice) pairs are grouped by expert on the device (nothing is read back, so a decode step stays a
 replayable graph), the experts' products run over the groups, each pair's result lands in a float32 row of its
@@ -20,7 +24,7 @@ import torch
 
 from .. import kernels
 from ..config.spec import FeedForwardSpec
-from .base import ParamDecl, Part, register_feed_forward
+from .base import ParamDecl, Part, feed_forward_class, register_feed_forward
 from .linear import Linear
 
 
@@ -33,12 +37,21 @@ class MixtureOfExperts(Part):
         self.n_experts, self.top = int(o["experts"]), int(o["top"])
         self.groups, self.keep_groups = int(o.get("groups", 1)), int(o.get("keep_groups", o.get("groups", 1)))
         self.group_best = int(o.get("group_best", 2))
-        if o.get("score", "sigmoid") not in ("sigmoid", "softmax"):
-            raise ValueError(f"moe: router score {o.get('score')!r} is not known (sigmoid, softmax)")
-        self.softmax = o.get("score", "sigmoid") == "softmax"
+        if o.get("score", "sigmoid") not in self.SCORES:
+            raise ValueError(f"moe: router score {o.get('score')!r} is not known ({', '.join(self.SCORES)})")
+        self.softmax = self.SCORES[o.get("score", "sigmoid")]
         self.renormalize = bool(o.get("renormalize", False))
-        if spec.activation != "silu":
-            raise ValueError(f"moe: expert activation {spec.activation!r} is not known (silu)")
+        if spec.activation not in ("silu", "swish_clamped"):
+            raise ValueError(f"moe: expert activation {spec.activation!r} is not known (silu, swish_clamped)")
+        # the clamped form: a positive limit switches the kernels' silu to it
+        self.limit = float(o.get("limit", 0.0)) if spec.activation == "swish_clamped" else 0.0
+        self.slope = float(o.get("slope", 1.0)) if spec.activation == "swish_clamped" else 1.0
+        if spec.activation == "swish_clamped" and not self.limit > 0.0:
+            raise ValueError("moe: the clamped activation needs a positive limit")
+        if self.softmax == 2 and (o.get("correction") or int(o.get("groups", 1)) != 1):
+            raise ValueError("moe: the softmax over the chosen logits goes with neither a correction nor groups")
+        shared = o.get("shared")
+        self.shared = feed_forward_class(shared.kind)(shared, dtype, device) if shared is not None else None
         E, G = self.n_experts, self.groups
         if E % G or not 1 <= self.keep_groups <= G or not 1 <= self.top <= self.keep_groups * (E // G):
             raise ValueError(f"moe: {E} experts in {G} groups of which {self.keep_groups} are kept cannot give "
@@ -62,6 +75,10 @@ class MixtureOfExperts(Part):
             p[f"e{e}.gate.weight"] = ParamDecl((ff, d))
             p[f"e{e}.up.weight"] = ParamDecl((ff, d))
             p[f"e{e}.down.weight"] = ParamDecl((d, ff))
+        shared = o.get("shared")
+        if shared is not None:
+            for name, decl in feed_forward_class(shared.kind).declare(shared).items():
+                p["shared." + name] = decl
         return p
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -77,9 +94,15 @@ class MixtureOfExperts(Part):
         self.gate_up = torch.stack([join(tensors[f"e{e}.gate.weight"].to(wide), tensors[f"e{e}.up.weight"].to(wide))
                                     for e in range(E)]).contiguous()
         self.down = torch.stack([tensors[f"e{e}.down.weight"].to(wide) for e in range(E)]).contiguous()
+        if self.shared is not None:
+            self.shared.bind({k[len("shared."):]: v for k, v in tensors.items() if k.startswith("shared.")})
+
+    SCORES = {"sigmoid": 0, "softmax": 1, "softmax_chosen": 2}
 
     def kernel_libraries(self) -> Tuple[str, ...]:
         libs = ("moe",) + (kernels.fast_gemm_libraries() if self.interleaved else ())
+        if self.shared is not None:
+            libs += self.shared.kernel_libraries()
         return libs + (self.router.libraries(self.dtype) if self.router is not None else ("gemm_generic",))
 
     def forward(self, step, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True):
@@ -115,11 +138,18 @@ class MixtureOfExperts(Part):
         if (self.interleaved and T >= self.TENSOR_CORE_TOKENS and not single
                 and self._on_tensor_cores(step, h, offs, order, act, y)):
             kernels.moe_combine(y, weights, residual, accumulate, place=place)
-            return None
+            return self._add_shared(step, h, residual)
         skinny = T <= self.SKINNY_TOKENS or single or (self.interleaved and T < self.TENSOR_CORE_TOKENS)
-        kernels.moe_grouped(h, self.gate_up, act, True, P, top, *groups, interleaved=self.interleaved, skinny=skinny)
+        kernels.moe_grouped(h, self.gate_up, act, True, P, top, *groups, interleaved=self.interleaved, skinny=skinny,
+                            limit=self.limit, slope=self.slope)
         kernels.moe_grouped(act, self.down, y, False, P, top, *groups, skinny=skinny)
         kernels.moe_combine(y, weights, residual, accumulate)
+        return self._add_shared(step, h, residual)
+
+    def _add_shared(self, step, h: torch.Tensor, residual: torch.Tensor):
+        """The shared feed-forward's output, added to what the experts left in ``residual``."""
+        if self.shared is not None:
+            self.shared.forward(step, h, residual)
         return None
 
     TENSOR_CORE_TOKENS = 128      # from this many tokens on a prompt step's experts run on the tensor cores
@@ -142,7 +172,7 @@ class MixtureOfExperts(Part):
         self._host_offs.copy_(offs, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         host = ctypes.c_void_p(self._host_offs.data_ptr())
-        if not kernels.gemm_tc_groups(rows, self.gate_up, act, host, glu="silu"):
+        if not kernels.gemm_tc_groups(rows, self.gate_up, act, host, glu="silu", limit=self.limit, slope=self.slope):
             return False
         return kernels.gemm_tc_groups(act, self.down, y, host)
 

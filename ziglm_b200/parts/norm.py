@@ -28,7 +28,8 @@ class RMSNorm(Part):
 
     @classmethod
     def declare(cls, spec: NormSpec) -> Dict[str, ParamDecl]:
-        return {"weight": ParamDecl((spec.width,), init="ones")}
+        # a weight kept as the gain minus one lies around zero
+        return {"weight": ParamDecl((spec.width,), init="zeros" if spec.options.get("unit_offset") else "ones")}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
@@ -50,6 +51,13 @@ class RMSNorm(Part):
         stream by the kernel that takes it."""
         kernels.rmsnorm_rows(branch, self.weight, residual, self.eps, add=True, weight_offset=self.weight_offset)
 
+    def add_scaled(self, step, branch: torch.Tensor, residual: torch.Tensor, mult: float,
+                   rows_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """residual += mult * norm(branch), both float32 [T, width]; with ``rows_out`` the new rows of the residual
+        are also left there in its type (what a sublayer that reads the residual itself takes next)."""
+        kernels.norm_add_scaled(branch, self.weight, self.eps, mult, residual, rows_out, weight_offset=self.weight_offset)
+        return rows_out
+
     def add_normed_then(self, step, branch: torch.Tensor, residual: torch.Tensor, nxt: "RMSNorm",
                         name: str = "norm_out") -> torch.Tensor:
         """residual += norm(branch), and the rows of the norm ``nxt`` of the new residual (the input of the next
@@ -68,4 +76,30 @@ class RMSNorm(Part):
         return out
 
 
+class CastRows(Part):
+    """No norm at all: the rows of the float32 residual in the step's storage type.  It stands where an arrangement
+    whose sublayers read the residual stream itself has no norm before a sublayer; it owns no tensor."""
+    fusable = False
+
+    def __init__(self, spec: Optional[NormSpec], dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        self.eps = 0.0
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        return ("elementwise",)
+
+    def forward(self, step, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+                name: str = "cast_out") -> torch.Tensor:
+        if rows is not None:
+            raise ValueError("cast: a choice of rows is not supported")
+        if out is None:
+            if self.dtype == torch.float32:
+                return x
+            out = step.ws.buf(name, tuple(x.shape), self.dtype)
+        kernels.convert(x, out)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("cast", CastRows)

@@ -105,9 +105,16 @@ class Rope(Part):
         self.rotary_dim = spec.rotary_dim
         self.inv_freq = inverse_frequencies(spec.rotary_dim, spec.theta, spec.scaling).to(device)
         self.factor = score_factor(spec.scaling)
+        # ``amplitude_in_table``: the factor stays with the cosines and sines (``amplitude``; the kernel that turns
+        # the heads multiplies by it), for mixers that cannot move it into the scores: a norm follows the rotation,
+        # or only a part of the head is rotated
+        self.in_table = bool(spec.options.get("amplitude_in_table"))
+        self.amplitude = self.factor if self.in_table else 1.0
 
     def score_scale(self, head_dim: int) -> float:
         """What the mixer multiplies its scores by on behalf of this encoding."""
+        if self.in_table:
+            return 1.0
         if self.factor != 1.0 and head_dim != self.rotary_dim:
             raise ValueError("a rope scaling that scales queries and keys needs the whole head to be rotated "
                              f"(rotary_dim {self.rotary_dim}, head size {head_dim})")

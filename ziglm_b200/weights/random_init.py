@@ -118,6 +118,8 @@ def random_tensor(name: str, decl: ParamDecl, seed: int, dtype: torch.dtype, dev
         return torch.zeros(decl.shape, dtype=torch.int32, device=device)
     if decl.init == "ones":
         mean, spread = 1.0, float(norm_jitter)
+    elif decl.init == "zeros":
+        mean, spread = 0.0, float(norm_jitter)
     else:
         mean, spread = 0.0, float(std)
     if spread == 0.0:
