@@ -68,6 +68,26 @@ SHAPES["tumatar-1b"] = _tumatar(2048, 128256, 8, 16, 8192, 16, 2048)
 SHAPES["tumatar-8b"] = _tumatar(4096, 128256, 16, 32, 14336, 16, 3584)
 
 
+def _tikalix(width: int, vocab: int, pairs: int, heads: int, kv_heads: int, dim: int, ff: int, experts: int,
+             expert_ff: int) -> Dict[str, Any]:
+    """A Tikalix stack of ``pairs`` times (attention + dense feed-forward, attention + experts with a shared one) with
+    the heads of the Llama shape of that width: keys and values of one size, the whole head rotated and stretched
+    fourfold, a soft cap of 30."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+             "rot": {"dims": dim, "base": 500000.0, "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    dense = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}
+    moe = {"type": "attention", "mixer": mixer,
+           "mlp": {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "top": 2},
+                   "shared": {"ff": expert_ff, "limit": 7.0}}}
+    return {"architecture": "Tikalix", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "layers": [copy.deepcopy(x) for _ in range(pairs) for x in (dense, moe)]}
+
+
+SHAPES["tikalix-1b"] = _tikalix(2048, 128256, 8, 32, 8, 64, 8192, 16, 2048)
+SHAPES["tikalix-8b"] = _tikalix(4096, 128256, 16, 32, 8, 128, 14336, 16, 3584)
+
+
 def shape(name: str) -> Dict[str, Any]:
     """A copy of the named config.json dictionary."""
     try:
