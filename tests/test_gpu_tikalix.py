@@ -135,7 +135,7 @@ def test_a_far_key_among_hundreds(dn, softcap):
     plain = TC.plain(cfg, w, dn)
     want = plain.forward(toks)
     without = plain.forward(toks[1:])
-    assert (want[-1] - without[-1]).abs().max() > 0.2 * want[-1].abs().max()      # the far key matters
+    assert (want[-1] - without[-1]).abs().max() > (0.1 if softcap else 0.2) * want[-1].abs().max()      # the far key matters
     other = {**cfg, "layers": [{**cfg["layers"][0], "mixer": {**cfg["layers"][0]["mixer"],
                                                                 "softcap": None if softcap else 6.0}}]}
     uncapped = TC.plain(other, w, dn).forward(toks)
