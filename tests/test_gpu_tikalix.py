@@ -26,7 +26,7 @@ class Zoo:
     def get(self, name, dn):
         key = (name, dn)
         if key not in self.made:
-            eng, cfg, w = TC.build(TC.config(name), 11, dn)
+            eng, cfg, w = TC.build(TC.for_type(TC.config(name), dn), 11, dn)
             reqs = [random_tokens(n, cfg["vocab"], 500 + n) for n in (1, 2, 63, 64, 65, 130, 201)]
             plain = TC.plain(cfg, w, dn)
             want = [plain.forward(r) for r in reqs]
@@ -198,7 +198,7 @@ def test_every_option_left_out(dn):
 @pytest.mark.parametrize("name,dn", [("A", "float32"), ("B", "bfloat16")])
 def test_greedy_generation_through_the_entry_point(name, dn):
     from ziglm_b200 import GenerationOptions, SamplerParams
-    eng, cfg, w = TC.build(TC.config(name), 5, dn, std=0.3)       # large weights: well separated logits
+    eng, cfg, w = TC.build(TC.for_type(TC.config(name), dn), 5, dn, std=0.3)       # large weights: well separated logits
     prompts = [random_tokens(n, cfg["vocab"], 70 + n) for n in (3, 40, 9)]
     results, stats = eng.generate(prompts, GenerationOptions(max_tokens=8, ignore_eos=True,
                                                              sampler=SamplerParams(greedy=True)))

@@ -73,7 +73,8 @@ def test_rotation_unit_norm_and_cache_write(dtype, H, G, hd, rot, norm_dim, scal
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,hd,cap", [(6, 2, 40, 3.0), (4, 1, 64, 20.0), (5, 5, 24, 0.5), (3, 1, 128, None)])
+@pytest.mark.parametrize("H,G,hd,cap", [(6, 2, 40, 3.0), (4, 1, 64, 20.0), (5, 5, 24, 0.5), (3, 1, 128, None), (8, 2, 128, 5.0),
+                                        (2, 2, 64, 1.5)])
 def test_attention_with_a_soft_cap(dtype, H, G, hd, cap):
     """Prompts of two sequences (one continued) and then a decoded token each, against the formula; the queries are
     large enough for the cap to bite."""

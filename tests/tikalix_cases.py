@@ -79,6 +79,16 @@ def config(name: str) -> dict:
     return copy.deepcopy(CONFIGS[name])
 
 
+def for_type(cfg: dict, dn: str) -> dict:
+    """In bfloat16 the factors on the scores are halved: with a sharp softmax a rounding that moves a score moves the
+    residual stream enough for routers further up to send tokens to other experts, in the plain implementation's own
+    bfloat16 roundings too, and a comparison row by row then says little.  float32 keeps the sharp scores."""
+    if dn == "bfloat16":
+        for layer in cfg["layers"]:
+            layer["mixer"]["scale"] *= 0.5
+    return cfg
+
+
 def lively(w: Dict[str, torch.Tensor]) -> None:
     """Biases of the size of the projections' outputs (a lost bias shows), and routers with larger weights (logits
     well apart: a close call of the router is rare)."""

@@ -65,6 +65,8 @@ struct FmArgs {
     __nv_bfloat16* out;
     int n_heads, n_kv;
     float scale_log2;
+    float cap_in2;       // soft cap c > 0: 2 log2(e) * scale / c, so that 2^(raw * cap_in2) = exp(2 * raw * scale / c)
+    float cap_log2;      // c * log2(e), or 0: no cap
     int window;
     const int* block_table;
     int bt_stride;
@@ -77,12 +79,24 @@ struct FmArgs {
 // half.  Returns the factor by which the running sum was rescaled; updates m (reference maximum, base 2) and l.
 template <int HD, int NP>
 __device__ __forceinline__ float softmax_row(uint32_t t_s, uint32_t t_o, bool full, int lo_vis, int hi_vis, float scale,
-                                             float neg_big, int lt, float& m, float& l) {
+                                             float neg_big, int lt, float& m, float& l, float cap_in2, float cap_log2) {
     constexpr int N = NP * FM_PAGE;
     uint32_t v[N];
 #pragma unroll
     for (int c = 0; c < N / 32; ++c) tmem_ld32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
     tmem_ld_wait();
+    if (cap_log2 > 0.f) {
+        // a soft cap: the score s (raw * scale) becomes c tanh(s / c), with tanh(z) = 1 - 2 / (e^(2z) + 1) from one
+        // exponential and one reciprocal (accurate to a few units of the last place, which the approximate
+        // tanh instruction is not); the scores then are in base 2 already
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            float t;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(__uint_as_float(v[i]) * cap_in2));
+            v[i] = __float_as_uint(fmaf(-cap_log2, __fdividef(2.0f, t + 1.0f), cap_log2));
+        }
+        scale = 1.0f;
+    }
     float mx8[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) mx8[i] = neg_big;
@@ -377,9 +391,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             // registers between the maximum and the exponentials, and the stores of P are waited for once.
             float corr;
             if (np == FM_NP)
-                corr = softmax_row<HD, FM_NP>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l);
+                corr = softmax_row<HD, FM_NP>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l, a.cap_in2, a.cap_log2);
             else
-                corr = softmax_row<HD, 1>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l);
+                corr = softmax_row<HD, 1>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l, a.cap_in2, a.cap_log2);
             (void)corr;
             tmem_st_wait();
             tc_fence_before_sync();
@@ -513,9 +527,10 @@ using namespace zlm;
 
 // Prompt attention: B sequences with cu_seqlens[B+1] new tokens each after past_lens[b] cached ones.
 // q: bf16 [T, q_row_stride], the query heads first in each row; out: bf16 [T, n_heads * hd].
+// softcap c > 0: the scaled scores become c tanh(score / c); 0: none.
 ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long total_tokens, void* out, int B,
-                                          int max_new, int n_heads, int n_kv, int hd, float scale, int window,
-                                          const int* cu_seqlens, const int* past_lens, const int* block_table,
+                                          int max_new, int n_heads, int n_kv, int hd, float scale, float softcap,
+                                          int window, const int* cu_seqlens, const int* past_lens, const int* block_table,
                                           int bt_stride, const void* k_pages, const void* v_pages, long n_pages,
                                           int page_size, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
@@ -539,6 +554,8 @@ ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long
     a.n_heads = n_heads;
     a.n_kv = n_kv;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.cap_in2 = softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f;
+    a.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     a.window = window;
     a.block_table = block_table;
     a.bt_stride = bt_stride;

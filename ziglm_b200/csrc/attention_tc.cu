@@ -104,8 +104,8 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[HD / 16][4], const _
 template <int HD, int NT, bool FULL>
 __device__ __forceinline__ void page_step(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, uint32_t v_tile, int key0,
                                           int gkey0, int lim_lo, int lim_hi, int start_lo, int start_hi,
-                                          float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HD / 8][4],
-                                          int lane) {
+                                          float scale_log2, float cap_in2, float cap_log2, float (&m)[2],
+                                          float (&l)[2], float (&o)[HD / 8][4], int lane) {
     const int gid = lane >> 2, tid4 = lane & 3, mi = lane >> 3, r8 = lane & 7;
     float s[NT][4];
 #pragma unroll
@@ -121,6 +121,16 @@ __device__ __forceinline__ void page_step(const uint32_t (&qf)[HD / 16][4], uint
             mma_16816(s[2 * np], qf[ks], kf[0], kf[1]);
             mma_16816(s[2 * np + 1], qf[ks], kf[2], kf[3]);
         }
+    }
+    if (cap_log2 > 0.f) {
+        // a soft cap: the score (raw * scale) becomes c tanh(score / c), tanh(z) = 1 - 2 / (e^(2z) + 1) from one
+        // exponential and one division; the result is in base 2 already
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                s[nt][i] = fmaf(-cap_log2, __fdividef(2.0f, fast_exp2(s[nt][i] * cap_in2) + 1.0f), cap_log2);
+        scale_log2 = 1.0f;
     }
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -187,6 +197,8 @@ struct AtcCommon {
     long q_row_stride;
     int n_heads, n_kv;
     float scale_log2;
+    float cap_in2;       // soft cap c > 0: 2 log2(e) * scale / c; else 0
+    float cap_log2;      // c * log2(e), or 0: no cap
     int window;
     const int* block_table;
     int bt_stride;
@@ -288,10 +300,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
             if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
             if (p * PAGE >= start && p * PAGE + PAGE - 1 <= pos)
                 page_step<HD, 2, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
-                                       pos, pos, start, start, a.scale_log2, m, l, o, lane);
+                                       pos, pos, start, start, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
             else
                 page_step<HD, 2, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
-                                        pos, pos, start, start, a.scale_log2, m, l, o, lane);
+                                        pos, pos, start, start, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
@@ -671,10 +683,10 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
             if (!landed) break;
             if (p * PAGE >= start && p * PAGE + PAGE - 1 <= pos)
                 page_step<HD, 2, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
-                                       pos, pos, start, start, a.scale_log2, m, l, o, lane);
+                                       pos, pos, start, start, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
             else
                 page_step<HD, 2, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
-                                        pos, pos, start, start, a.scale_log2, m, l, o, lane);
+                                        pos, pos, start, start, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
@@ -929,10 +941,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const bool full = p * PAGE + PAGE - 1 <= w_first && p * PAGE >= w_last_start && w_rows_all;
             if (full)
                 page_step<HD, 8, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, 0, p * PAGE, lim_lo, lim_hi,
-                                       st_lo, st_hi, a.scale_log2, m, l, o, lane);
+                                       st_lo, st_hi, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
             else
                 page_step<HD, 8, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, 0, p * PAGE, lim_lo, lim_hi,
-                                        st_lo, st_hi, a.scale_log2, m, l, o, lane);
+                                        st_lo, st_hi, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * s);
@@ -1026,7 +1038,7 @@ static int set_smem(Kern kern, int bytes, bool* done) {
 
 static int fill_common(AtcCommon* a, CUtensorMap* mk, CUtensorMap* mv, const void* q, long q_row_stride, int n_heads,
                        int n_kv, int hd, float scale, int window, const int* block_table, int bt_stride,
-                       const void* k_pages, const void* v_pages, long n_pages, int page_size) {
+                       const void* k_pages, const void* v_pages, long n_pages, int page_size, float softcap = 0.f) {
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size != PAGE) return ZLM_ERR_BAD_ARG;
     if (hd != 64 && hd != 128) return ZLM_ERR_UNSUPPORTED;
     if (((uintptr_t)q % 4) || (q_row_stride % 2) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16))
@@ -1040,6 +1052,8 @@ static int fill_common(AtcCommon* a, CUtensorMap* mk, CUtensorMap* mv, const voi
     a->n_heads = n_heads;
     a->n_kv = n_kv;
     a->scale_log2 = scale * 1.4426950408889634f;
+    a->cap_in2 = softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f;
+    a->cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     a->window = window;
     a->block_table = block_table;
     a->bt_stride = bt_stride;
@@ -1054,7 +1068,7 @@ using namespace zlm;
 // Decode-style attention: every token is a tile of its own (its query heads grouped by kv head).
 // part_o: float [T * n_heads * n_splits * hd], part_ml: float [T * n_heads * n_splits * 2] (scratch).
 ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out, int T, int n_heads, int n_kv, int hd,
-                                    float scale, int window, const int* positions, const int* seq_of_token,
+                                    float scale, float softcap, int window, const int* positions, const int* seq_of_token,
                                     const int* block_table, int bt_stride, const void* k_pages, const void* v_pages,
                                     long n_pages, int page_size, int n_splits, float* part_o, float* part_ml,
                                     cudaStream_t stream) {
@@ -1064,7 +1078,7 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
     AtcCommon a;
     CUtensorMap mk, mv;
     int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
-                         k_pages, v_pages, n_pages, page_size);
+                         k_pages, v_pages, n_pages, page_size, softcap);
     if (rc) return rc;
     dim3 grid(n_splits, n_kv, T);
     using CFG128 = DecodeCfg<128>;
@@ -1142,7 +1156,7 @@ ZLM_EXPORT long zlm_attention_decode_flat_scratch(int T, int n_heads, int n_kv, 
 }
 
 ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void* out, int T, int n_heads, int n_kv,
-                                         int hd, float scale, int window, const int* positions,
+                                         int hd, float scale, float softcap, int window, const int* positions,
                                          const int* seq_of_token, const int* block_table, int bt_stride,
                                          const void* k_pages, const void* v_pages, long n_pages, int page_size,
                                          int n_blocks, int* counters, float* scratch, long scratch_floats,
@@ -1162,7 +1176,7 @@ ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void*
     AtcCommon a;
     CUtensorMap mk, mv;
     int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
-                         k_pages, v_pages, n_pages, page_size);
+                         k_pages, v_pages, n_pages, page_size, softcap);
     if (rc) return rc;
     const int group = n_heads / n_kv;
     int smem = 0;
@@ -1184,14 +1198,14 @@ ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void*
 
 // Prompt attention: B sequences with cu_seqlens[B+1] new tokens each after past_lens[b] cached ones.
 ZLM_EXPORT int zlm_attention_prefill(const void* q, long q_row_stride, void* out, int B, int max_new, int n_heads,
-                                     int n_kv, int hd, float scale, int window, const int* cu_seqlens,
+                                     int n_kv, int hd, float scale, float softcap, int window, const int* cu_seqlens,
                                      const int* past_lens, const int* block_table, int bt_stride, const void* k_pages,
                                      const void* v_pages, long n_pages, int page_size, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
     AtcCommon a;
     CUtensorMap mk, mv;
     int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
-                         k_pages, v_pages, n_pages, page_size);
+                         k_pages, v_pages, n_pages, page_size, softcap);
     if (rc) return rc;
     dim3 grid((max_new + 63) / 64, n_heads, B);
     if (grid.y > 65535 || grid.z > 65535) return ZLM_ERR_UNSUPPORTED;
@@ -1316,6 +1330,8 @@ ZLM_EXPORT int zlm_attention_decode_noalloc(const void* q, long q_row_stride, vo
     a.n_heads = n_heads;
     a.n_kv = n_kv;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.cap_in2 = 0.f;
+    a.cap_log2 = 0.f;
     a.window = window;
     a.block_table = block_table;
     a.bt_stride = bt_stride;

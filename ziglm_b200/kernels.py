@@ -103,22 +103,22 @@ _PROTOTYPES = {
         "zlm_attention_general_scratch": [c_int, c_int, c_int, c_int, c_int],
     },
     "attention_tc": {
-        "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+        "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                  c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
                                  c_void_p, c_void_p],
-        "zlm_attention_decode_flat": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+        "zlm_attention_decode_flat": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
                                       c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p],
         "zlm_attention_decode_flat_blocks": [c_int, c_int, c_int, c_int],
         "zlm_attention_decode_flat_scratch": [c_int, c_int, c_int, c_int, c_int],
-        "zlm_attention_prefill": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+        "zlm_attention_prefill": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "zlm_attention_tc_status": [c_void_p],
         "zlm_attention_tc_wait_selftest": [c_int, c_void_p, c_void_p],
     },
     "attention_fmha": {
         "zlm_attention_prefill_fmha": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                       c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int,
+                                       c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int,
                                        c_void_p],
         "zlm_attention_fmha_status": [c_void_p],
         "zlm_attention_fmha_wait_selftest": [c_int, c_void_p, c_void_p],
@@ -726,7 +726,7 @@ def _tc_attention_ok(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int,
 def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
                      window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                      block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
-                     n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor) -> bool:
+                     n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor, softcap: float = 0.0) -> bool:
     """Tensor-core attention for steps of one token per sequence (bf16, head size 64 or 128).
 
     Each token's query heads are grouped by key/value head so that the cache is read once per group; the keys
@@ -747,7 +747,8 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: i
     if part_o.numel() < T * n_heads * n_splits * head_dim or part_ml.numel() < T * n_heads * n_splits * 2:
         raise KernelError("attention_decode: the scratch is too small for this many splits")
     status = _fn("attention_tc", "zlm_attention_decode")(
-        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, int(window or 0),
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, float(softcap or 0.0),
+        int(window or 0),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
         k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_splits, part_o.data_ptr(),
         part_ml.data_ptr(), _stream())
@@ -773,7 +774,7 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
                           window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                           block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
                           n_blocks: int, counters: torch.Tensor, scratch: torch.Tensor,
-                          rope: Optional[Tuple[Optional[torch.Tensor], int, bool]] = None) -> bool:
+                          rope: Optional[Tuple[Optional[torch.Tensor], int, bool]] = None, softcap: float = 0.0) -> bool:
     """Tensor-core attention for steps of one token per sequence, with the pages of all sequences of the
     step divided evenly over ``n_blocks`` blocks (one resident wave), whatever the sequences' lengths.  One
     launch: the block that finishes a sequence's last piece merges the pieces.
@@ -816,7 +817,8 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
         if qkv.shape[1] < (n_heads + (2 * n_kv if store else 0)) * head_dim:
             raise KernelError("attention_decode_flat: the rows must hold the key and value heads to be stored")
     status = _fn("attention_tc", "zlm_attention_decode_flat")(
-        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, int(window or 0),
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, float(softcap or 0.0),
+        int(window or 0),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
         k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_blocks, counters.data_ptr(),
         scratch.data_ptr(), scratch.numel(), fused, int(bool(store)), int(rot), _ptr(inv_freq), _stream())
@@ -831,7 +833,7 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
                       head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
                       past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                      v_pages: torch.Tensor, page_size: int) -> bool:
+                      v_pages: torch.Tensor, page_size: int, softcap: float = 0.0) -> bool:
     """Tensor-core attention for prompt steps: sequence b brings tokens cu_seqlens[b]..cu_seqlens[b+1] of the
     packed stream after past_lens[b] cached ones (bf16, head size 64 or 128).  False if refused."""
     _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
@@ -847,7 +849,7 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new
         raise KernelError("attention_prefill: sequence arrays are too short")
     status = _fn("attention_tc", "zlm_attention_prefill")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
-        int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
+        float(softcap or 0.0), int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, _stream())
     if status == -2:
         return False
@@ -858,7 +860,7 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new
 def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
                            head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
                            past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                           v_pages: torch.Tensor, page_size: int) -> bool:
+                           v_pages: torch.Tensor, page_size: int, softcap: float = 0.0) -> bool:
     """Prompt attention on the tcgen05 tensor cores (tiles of 128 queries, accumulators in tensor memory); same
     arguments as :func:`attention_prefill`.  False if refused."""
     _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
@@ -874,7 +876,7 @@ def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, ma
         raise KernelError("attention_prefill_fmha: sequence arrays are too short")
     status = _fn("attention_fmha", "zlm_attention_prefill_fmha")(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
-        int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
+        float(softcap or 0.0), int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, _stream())
     if status == -2:
         return False
@@ -933,7 +935,7 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
               window: Optional[int], io, softcap: float = 0.0) -> None:
     """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``softcap`` c > 0:
     the scaled scores become c * tanh(score / c)."""
-    if not softcap and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
+    if _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
         if n_blocks > 0:
             need = attention_decode_flat_scratch(step.n_tokens, n_heads, n_kv, head_dim, n_blocks)
@@ -941,7 +943,7 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
             counters = step.ws.buf("attn_flat_counters", (step.n_tokens * n_kv,), torch.int32, zeros=True)
             if attention_decode_flat(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions,
                                      step.seq_of_token, io.block_table, io.k_pages, io.v_pages, io.page_size,
-                                     n_blocks, counters, scratch):
+                                     n_blocks, counters, scratch, softcap=softcap):
                 return
         if step.single_token:
             n_splits = decode_splits(step.n_tokens, n_kv, step.max_total, io.page_size)
@@ -949,15 +951,15 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
             part_ml = step.ws.buf("attn_part_ml", (step.n_tokens * n_heads * n_splits * 2,), torch.float32)
             if attention_decode(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions,
                                 step.seq_of_token, io.block_table, io.k_pages, io.v_pages, io.page_size, n_splits,
-                                part_o, part_ml):
+                                part_o, part_ml, softcap=softcap):
                 return
         else:
             # prompts: the tcgen05 kernel (tiles of 128 queries); a handful of tokens: the 64-row mma.sync one
             args = (qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window, step.cu_seqlens,
                     step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size)
-            if step.max_new >= 16 and attention_prefill_fmha(*args):
+            if step.max_new >= 16 and attention_prefill_fmha(*args, softcap=softcap):
                 return
-            if attention_prefill(*args):
+            if attention_prefill(*args, softcap=softcap):
                 return
     max_keys = min(step.max_total, window) if window else step.max_total
     need = attention_general_scratch(step.n_tokens, n_heads, n_kv, head_dim, max_keys)
@@ -968,8 +970,6 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
 
 def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1, softcap: float = 0.0):
     """The sources of the tensor-core attention kernels if they take this shape, else nothing (the plain kernel runs)."""
-    if softcap:
-        return ()
     return ("attention_tc", "attention_fmha") if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
 
 
