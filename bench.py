@@ -9,6 +9,7 @@
     python bench.py --case float32 [--layers L]    the 8B shape in true 32-bit: a 2,048-token prompt, decode at batch 1 and 8
     python bench.py --case reference-kernels [--context C]     the reference's CUDA kernels alone, if they were built
     python bench.py --case tumatar [--shape 1b|8b] [--layers L]    the Tumatar design beside Llama at equal width, its kernels alone
+    python bench.py --case tikalix [--shape 1b|8b] [--layers L]    the Tikalix design beside Llama at equal width, its kernels alone
 
 A "step" is one decode step of a batch of 8 sequences at a context of 4096
 tokens.  ``value`` is decoded tokens a second, timed on the device with CUDA
@@ -554,6 +555,166 @@ def run_tumatar(args):
     return 0
 
 
+def run_tikalix(args):
+    """The Tikalix design beside the Llama shape of the same width and heads, with random weights: a prompt of
+    ``--prompt-tokens`` and decode steps of ``--batch`` sequences at ``--context``, ``--layers`` layers of each
+    (default 4), and every kernel the design adds or changes, alone, against its own roofline (the larger of bytes /
+    measured copy bandwidth and FLOPs / measured bf16 peak), each beside the library's like kernel timed in the same
+    run on operands of the same size."""
+    import ctypes
+    import torch
+    from types import SimpleNamespace
+    from ziglm_b200 import kernels
+    from ziglm_b200.config.shapes import shape
+    from ziglm_b200.engine.workspace import Workspace
+    from ziglm_b200.parts.base import LayerIO
+    torch.cuda.set_device(0)
+    pk = peaks()
+    size = "8b" if args.shape == "8b" else "1b"
+    layers = args.layers or 4
+    T, batch, context = args.prompt_tokens, args.batch, args.context
+    max_seq = max(context, T) + 64
+    gen = torch.Generator().manual_seed(7)
+    out = {"case": "tikalix", "width_of": "llama-" + size, "dtype": "bf16", "layers": layers, "prompt_tokens": T,
+           "batch": batch, "context": context, "data": "synthetic", "l2": "a 256 MiB buffer is rewritten before every timed call",
+           "peaks": pk["source"], "models": {}}
+    for name in ("tikalix-" + size, "llama-" + size):
+        cfg = shape(name)
+        if "layers" in cfg:
+            cfg["layers"] = cfg["layers"][:layers]
+            vocab = cfg["vocab"]
+        else:
+            cfg["num_hidden_layers"] = layers
+            cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], max_seq)
+            vocab = cfg["vocab_size"]
+        eng = _engine_for(cfg, "bfloat16", batch, max_seq)
+        ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        pre = _time_prompt(eng, ids(T), args.warmup, args.steps)
+        dec = _time_decode_at(eng, batch, context, args.warmup, args.steps, ids)
+        out["models"][name] = {"prefill_ms": round(pre, 3), "prefill_tok_s": round(T / pre * 1e3, 1),
+                               "decode_ms": round(dec, 4), "decode_tok_s": round(batch / dec * 1e3, 1)}
+        del eng
+        torch.cuda.empty_cache()
+    # ---- the kernels, alone
+    cfg = shape("tikalix-" + size)
+    d = cfg["width"]
+    mix, moe = cfg["layers"][0]["mixer"], cfg["layers"][1]["mlp"]
+    ff = cfg["layers"][0]["mlp"]["ff"]
+    H, G, hd, cap, scale = mix["heads"], mix["kv_heads"], mix["dim"], mix["softcap"], mix["scale"]
+    E, top, eff, limit = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"], moe["expert"]["limit"]
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    bf = lambda *sh: (torch.randn(*sh, device=dev) * 0.05).to(torch.bfloat16)
+    f32 = lambda *sh: torch.randn(*sh, device=dev) * 0.05
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = []
+
+    def report(what, like, ms, nbytes, flops):
+        floor = max(nbytes / hbm, flops / peak) * 1e3
+        rows.append({"kernel": what, "like": like, "ms": round(ms, 4), "roofline_ms": round(floor, 4),
+                     "frac_of_roofline": round(floor / ms, 4)})
+
+    def timed(fn):
+        return _timed(fn, args.warmup, args.steps, flush)
+
+    kernels.require(("elementwise", "attention", "attention_tc", "attention_fmha", "moe", "gemm_generic", "gemm_tc"))
+    page = 64
+    inv_freq = torch.rand(hd // 2, device=dev)
+    for n_tok, tag in ((T, f"prompt of {T}"), (batch, f"decode batch {batch}")):
+        decode = n_tok != T
+        past = context - 1 if decode else 0
+        n_seq = n_tok if decode else 1
+        per_seq = -(-(past + (1 if decode else T)) // page)
+        k_pages, v_pages = bf(n_seq * per_seq, G, page, hd), bf(n_seq * per_seq, G, page, hd)
+        table = torch.arange(n_seq * per_seq, dtype=torch.int32, device=dev).view(n_seq, per_seq)
+        new = [1] * n_seq if decode else [T]
+        cu = [0]
+        for n in new:
+            cu.append(cu[-1] + n)
+        step = SimpleNamespace(
+            n_tokens=n_tok, n_seqs=n_seq, single_token=decode, max_new=max(new), max_total=past + max(new),
+            positions=i32([past + i for n in new for i in range(n)]), seq_of_token=i32([b for b, n in enumerate(new) for _ in range(n)]),
+            cu_seqlens=i32(cu), past_lens=i32([past] * n_seq), total_lens=i32([past + n for n in new]), ws=Workspace(dev))
+        io = LayerIO(k_pages=k_pages, v_pages=v_pages, block_table=table, page_size=page)
+        # rotation + unit norm + cache write, beside the library's rotation + cache write
+        proj = bf(n_tok, (2 * H + 2 * G) * hd)
+        qkv = bf(n_tok, (H + 2 * G) * hd)
+        rope_bytes = n_tok * (H + G) * hd * 4 + n_tok * G * hd * 2 * 3
+        ms = timed(lambda: kernels.rope_store(qkv, H, G, hd, hd, inv_freq, step.positions, step.seq_of_token, table, k_pages,
+                                              v_pages, page))
+        report(f"rope_store (rotation + cache write), {tag}", "-", ms, rope_bytes, 0)
+        ms = timed(lambda: kernels.rope_norm_store(proj, H, G, hd, hd, inv_freq, 1.1, hd, 1e-6, step.positions,
+                                                   step.seq_of_token, table, k_pages, v_pages, page))
+        report(f"rope_norm_store (rotation + unit norm + cache write), {tag}", "rope_store", ms, rope_bytes, 0)
+        # attention with and without the soft cap
+        att_out = torch.empty(n_tok, H * hd, dtype=torch.bfloat16, device=dev)
+        if decode:
+            att_bytes, att_flops = n_seq * (past + 1) * G * hd * 2 * 2 + n_tok * H * hd * 4, 4.0 * n_tok * H * hd * (past + 1)
+        else:
+            att_bytes, att_flops = n_tok * (H + 2 * G) * hd * 2 + n_tok * H * hd * 2, 2.0 * H * hd * T * T
+        ms = timed(lambda: kernels.attention(step, qkv, att_out, H, G, hd, scale, None, io))
+        report(f"attention, {tag}", "-", ms, att_bytes, att_flops)
+        ms = timed(lambda: kernels.attention(step, proj, att_out, H, G, hd, scale, None, io, softcap=cap))
+        report(f"attention with a soft cap of {cap}, {tag}", "attention", ms, att_bytes, att_flops)
+        ms = timed(lambda: kernels.sigmoid_mul(att_out, proj[:, (H + 2 * G) * hd:], att_out))
+        report(f"sigmoid_mul (output gate), {tag}", "rmsnorm", ms, n_tok * H * hd * 6, 0)
+        # norms
+        xr, wn, yn = f32(n_tok, d), bf(d), torch.empty(n_tok, d, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: kernels.rmsnorm(xr, wn, yn, 1e-6))
+        report(f"rmsnorm, {tag}", "-", ms, n_tok * d * 6 + d * 2, 0)
+        res = f32(n_tok, d)
+        ms = timed(lambda: kernels.norm_add_scaled(xr, wn, 1e-6, 0.5, res, yn, weight_offset=1.0))
+        report(f"norm_add_scaled (norm behind a sublayer + residual sum + next rows), {tag}", "rmsnorm", ms,
+               n_tok * d * 14 + d * 2, 0)
+        # the dense feed-forward's first product with its activation, beside the gated product of as many rows
+        x, wu, act = bf(n_tok, d), bf(ff, d), torch.empty(n_tok, ff, dtype=torch.bfloat16, device=dev)
+        wg, actg = bf(ff, d), torch.empty(n_tok, ff // 2, dtype=torch.bfloat16, device=dev)
+        up_bytes, up_flops = n_tok * d * 2 + ff * d * 2 + n_tok * ff * 2, 2.0 * n_tok * d * ff
+        ms = timed(lambda: kernels.gemm_tc(x, wg, actg, glu="silu"))
+        report(f"gemm_tc gated silu ({ff} rows of weights), {tag}", "-", ms, up_bytes - n_tok * ff, up_flops)
+        ms = timed(lambda: kernels.gemm_tc_unary(x, wu, act, "relu2"))
+        report(f"gemm_tc_unary squared relu ({ff} rows of weights), {tag}", "gemm_tc gated silu", ms, up_bytes, up_flops)
+        # the experts
+        P = n_tok * top
+        h, z = bf(n_tok, d), f32(n_tok, E) * 40
+        ids_t = torch.empty(n_tok, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(n_tok, top, dtype=torch.float32, device=dev)
+        ms = timed(lambda: kernels.moe_route(z, None, top, 1, 1, 2, ids_t, wts, softmax_scores=1, renormalize=True))
+        report(f"moe_route softmax ({E} experts), {tag}", "-", ms, n_tok * (E * 4 + top * 8), 0)
+        ms = timed(lambda: kernels.moe_route(z, None, top, 1, 1, 2, ids_t, wts, softmax_scores=2))
+        report(f"moe_route softmax over the chosen ({E} experts), {tag}", "moe_route softmax", ms, n_tok * (E * 4 + top * 8), 0)
+        mt = kernels.moe_max_tiles(P, E)
+        e32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
+        offs, order, place, te, tr, nt = e32(E + 1), e32(P), e32(P), e32(mt), e32(mt), e32(1)
+        grp = (offs, order, te, tr, nt)
+        kernels.moe_group(ids_t.view(-1), E, offs, order, place, te, tr, nt)
+        wgu = bf(E, 2 * eff, d)
+        eact = torch.empty(P, eff, dtype=torch.bfloat16, device=dev)
+        used = min(E, P)
+        gu_bytes, gu_flops = used * 2 * eff * d * 2 + P * d * 2 + P * eff * 2, 2.0 * P * 2 * eff * d
+        if n_tok >= 128:
+            hrows = torch.empty(P, d, dtype=torch.bfloat16, device=dev)
+            kernels.moe_gather(h, order, top, hrows)
+            host_offs = offs.cpu()
+            hp = ctypes.c_void_p(host_offs.data_ptr())
+            ms = timed(lambda: kernels.gemm_tc_groups(hrows, wgu, eact, hp, glu="silu"))
+            report(f"gemm_tc per expert, gate/up silu ({eff} per expert), {tag}", "-", ms, gu_bytes, gu_flops)
+            ms = timed(lambda: kernels.gemm_tc_groups(hrows, wgu, eact, hp, glu="silu", limit=limit, slope=1.702))
+            report(f"gemm_tc per expert, gate/up clamped ({eff} per expert), {tag}", "gemm_tc per expert silu", ms, gu_bytes, gu_flops)
+        else:
+            ms = timed(lambda: kernels.moe_grouped(h, wgu, eact, True, P, top, *grp, interleaved=True, skinny=True))
+            report(f"moe_grouped gate/up silu, streaming ({eff} per expert), {tag}", "-", ms, gu_bytes, gu_flops)
+            ms = timed(lambda: kernels.moe_grouped(h, wgu, eact, True, P, top, *grp, interleaved=True, skinny=True,
+                                                   limit=limit, slope=1.702))
+            report(f"moe_grouped gate/up clamped, streaming ({eff} per expert), {tag}", "moe_grouped silu", ms, gu_bytes, gu_flops)
+        del k_pages, v_pages
+    out["kernels"] = rows
+    out["wait_errors"] = wait_errors(kernels)
+    print(json.dumps(out))
+    return 0
+
+
 def run_workload(args):
     """The two workloads beside the headline one, through ``Engine.generate`` (host token ids in, ids out):
 
@@ -773,11 +934,12 @@ def main():
                     help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--case", default="full",
                     choices=["full", "prefill", "decode", "workload-1b", "workload-13b", "float32", "reference-kernels",
-                             "tumatar"],
+                             "tumatar", "tikalix"],
                     help="full: the whole measurement; prefill / decode: that phase alone (for profilers and sweeps); "
                          "workload-1b / workload-13b: the two other workloads through Engine.generate; float32: the "
                          "8B shape in true 32-bit; reference-kernels: the reference's CUDA kernels alone, if built; tumatar: the "
-                         "Tumatar design beside the Llama shape of the same width (--shape 1b or 8b), and its kernels alone")
+                         "Tumatar design beside the Llama shape of the same width (--shape 1b or 8b), and its kernels alone; tikalix: "
+                         "the same for the Tikalix design")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="--case prefill/decode: layer sizes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="--case prefill/decode")
     ap.add_argument("--repeats", type=int, default=2, help="workload cases: timed repetitions after one warm-up")
@@ -801,6 +963,8 @@ def main():
         return run_float32(args)
     if args.case == "tumatar":
         return run_tumatar(args)
+    if args.case == "tikalix":
+        return run_tikalix(args)
     if args.case != "full":
         return run_case(args)
     return run_ours(args)

@@ -276,6 +276,121 @@ rope_norm_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_
     }
 }
 
+// The same for bf16 rows whose heads, rotated halves and strides are multiples of 8 elements: a thread moves 16
+// bytes at a time.  A head is shared by LPH lanes of a warp (a power of two that covers its units: rot/16 units of
+// 8 pairs of the rotation, then (hd - rot)/8 units of 8 elements that pass), so a warp works on 32/LPH heads at
+// once and the sum of squares is folded over those lanes alone.  Same arithmetic, element by element.
+__global__ void __launch_bounds__(RNS_WARPS * 32)
+rope_norm_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
+                           const float* __restrict__ inv_freq, float amplitude, int norm_dim, float norm_eps,
+                           const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                           const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pages,
+                           __nv_bfloat16* __restrict__ v_pages, int page_size, long page_stride, int lph) {
+    __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = positions[t];                       // positions, tables and frequencies are older than the step
+    const int half = rot / 2;
+    const bool turn = inv_freq != nullptr && half > 0;
+    if (turn) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            sin_s[i] = sn * amplitude;
+            cos_s[i] = cs * amplitude;
+        }
+    }
+    __nv_bfloat16* kdst = nullptr;
+    __nv_bfloat16* vdst = nullptr;
+    if (k_pages != nullptr && n_kv > 0) {
+        const int b = seq_of_token[t];
+        const int page = block_table[(long)b * bt_stride + pos / page_size];
+        const long off = (long)page * page_stride + (long)(pos % page_size) * hd;
+        kdst = k_pages + off;
+        vdst = v_pages + off;
+    }
+    __syncthreads();
+    pdl_wait();
+    __nv_bfloat16* row0 = qkv + (long)t * row_stride;
+    const long kv_head_stride = (long)page_size * hd;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int units_rot = turn ? rot / 16 : 0;
+    const int first_tail = turn ? rot : 0;
+    const int units = units_rot + (hd - first_tail) / 8;
+    const int hpw = 32 / lph;                                   // heads a warp holds at once
+    const int total_qk = n_heads + n_kv;
+    const int sub = lane % lph;
+    for (int head0 = (blockIdx.y * RNS_WARPS + warp) * hpw; head0 < total_qk; head0 += gridDim.y * RNS_WARPS * hpw) {
+        const int head = head0 + lane / lph;
+        const bool active = head < total_qk && sub < units;
+        const bool pair = active && sub < units_rot;
+        __nv_bfloat16* row = row0 + (long)head * hd;
+        const int i0 = pair ? sub * 8 : first_tail + (sub - units_rot) * 8;
+        float a[8], b[8];
+        float ss = 0.f;
+        if (active) {
+            const uint4 lo = *reinterpret_cast<const uint4*>(row + i0);
+            const __nv_bfloat162* lp = reinterpret_cast<const __nv_bfloat162*>(&lo);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 x = __bfloat1622float2(lp[k]);
+                a[2 * k] = x.x; a[2 * k + 1] = x.y;
+            }
+            if (pair) {
+                const uint4 hi = *reinterpret_cast<const uint4*>(row + i0 + half);
+                const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&hi);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 y = __bfloat1622float2(hp[k]);
+                    b[2 * k] = y.x; b[2 * k + 1] = y.y;
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float c = cos_s[i0 + k], sn = sin_s[i0 + k];
+                    const float u = a[k], v = b[k];
+                    a[k] = u * c - v * sn;
+                    b[k] = v * c + u * sn;
+                    if (i0 + half + k < norm_dim) ss = fmaf(b[k], b[k], ss);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (i0 + k < norm_dim) ss = fmaf(a[k], a[k], ss);
+        }
+        float inv = 1.0f;
+        if (norm_dim > 0) {
+            for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            inv = 1.0f / sqrtf(ss / (float)norm_dim + norm_eps);
+        }
+        if (active) {
+            __nv_bfloat16* d = (kdst && head >= n_heads) ? kdst + (long)(head - n_heads) * kv_head_stride : nullptr;
+            uint4 lo;
+            __nv_bfloat162* lp = reinterpret_cast<__nv_bfloat162*>(&lo);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) lp[k] = __floats2bfloat162_rn(a[2 * k] * inv, a[2 * k + 1] * inv);
+            *reinterpret_cast<uint4*>(row + i0) = lo;
+            if (d) *reinterpret_cast<uint4*>(d + i0) = lo;
+            if (pair) {
+                uint4 hi;
+                __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) hp[k] = __floats2bfloat162_rn(b[2 * k] * inv, b[2 * k + 1] * inv);
+                *reinterpret_cast<uint4*>(row + i0 + half) = hi;
+                if (d) *reinterpret_cast<uint4*>(d + i0 + half) = hi;
+            }
+        }
+    }
+    if (vdst) {
+        const int v_units = hd / 8;
+        const int n_threads = gridDim.y * blockDim.x;
+        for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < n_kv * v_units; idx += n_threads) {
+            const int h = idx / v_units, i = (idx % v_units) * 8;
+            *reinterpret_cast<uint4*>(vdst + (long)h * kv_head_stride + i) =
+                *reinterpret_cast<const uint4*>(row0 + (long)(total_qk + h) * hd + i);
+        }
+    }
+}
+
 // ------------------------------------------------------------ attention
 // The keys a token sees, [start, pos], are cut into parts of ATT_PART = 256 consecutive keys counted from
 // `start`.  Within a part warp w of a block takes the key blocks w and w + 4 of 32 keys: lane j scores key j of
@@ -616,7 +731,22 @@ ZLM_EXPORT int zlm_rope_norm_store(void* qkv, int dtype, long row_stride, int T,
         e = launch_pdl(rope_norm_store_kernel<float>, grid, dim3(RNS_WARPS * 32), 0, stream, (float*)qkv, row_stride,
                        n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions, seq_of_token,
                        block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size, page_stride);
-    else if (dtype == ZLM_BF16)
+    else if (dtype == ZLM_BF16 && hd % 8 == 0 && (inv_freq == nullptr || rot % 16 == 0) && row_stride % 8 == 0 &&
+             page_stride % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 &&
+             (uintptr_t)v_pages % 16 == 0 && hd / 8 <= 32) {
+        const int first_tail = (inv_freq != nullptr && rot > 0) ? rot : 0;
+        const int units = first_tail / 16 + (hd - first_tail) / 8;
+        int lph = 1;
+        while (lph < units) lph <<= 1;
+        const int per_block = RNS_WARPS * (32 / lph);
+        int vparts = (296 + T - 1) / T;
+        const int most = (n_heads + n_kv + per_block - 1) / per_block;
+        if (vparts > most) vparts = most;
+        if (vparts < 1) vparts = 1;
+        e = launch_pdl(rope_norm_store_vec_kernel, dim3(T, vparts), dim3(RNS_WARPS * 32), 0, stream, (__nv_bfloat16*)qkv,
+                       row_stride, n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions, seq_of_token,
+                       block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, page_stride, lph);
+    } else if (dtype == ZLM_BF16)
         e = launch_pdl(rope_norm_store_kernel<__nv_bfloat16>, grid, dim3(RNS_WARPS * 32), 0, stream, (__nv_bfloat16*)qkv,
                        row_stride, n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions,
                        seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size,
