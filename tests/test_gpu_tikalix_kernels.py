@@ -128,12 +128,16 @@ def test_attention_with_a_soft_cap(dtype, H, G, hd, cap):
 def test_gate_norm_behind_a_sublayer_and_squared_relu(dtype):
     from ziglm_b200 import kernels
     kernels.require(("elementwise",))
-    T, n = 9, 50
-    wide = _r(T, 3 * n + 8, seed=1, scale=2.0, dtype=dtype)
-    a, g = wide[:, :n], wide[:, 2 * n + 8:]
-    want = (a.float() * torch.sigmoid(g.float())).to(dtype)
-    kernels.sigmoid_mul(a, g, a)                                   # in place, strided rows
-    torch.testing.assert_close(a.float(), want.float(), **_tol(dtype, (1e-6, 1e-6), (1e-6, 1e-2)))
+    T = 9
+    for n in (50, 64):                                             # 64: sixteen bytes a thread in bfloat16
+        wide = _r(T, 3 * n + 8, seed=1, scale=2.0, dtype=dtype)
+        a, g = wide[:, :n], wide[:, 2 * n + 8:]
+        want = (a.float() * torch.sigmoid(g.float())).to(dtype)
+        rest = wide[:, n:].clone()
+        kernels.sigmoid_mul(a, g, a)                               # in place, strided rows
+        torch.testing.assert_close(a.float(), want.float(), **_tol(dtype, (1e-6, 1e-6), (1e-6, 1e-2)))
+        assert torch.equal(wide[:, n:], rest)
+    n = 50
     x = _r(T, n, seed=2, scale=3.0, dtype=dtype)
     y = torch.empty_like(x)
     kernels.unary_act(x, y, "relu2")

@@ -311,6 +311,27 @@ __global__ void sigmoid_mul_kernel(const T* __restrict__ a, long a_stride, const
     out[t * out_stride + i] = from_float<T>(to_float(a[t * a_stride + i]) * (1.0f / (1.0f + expf(-gv))));
 }
 
+// The same for bf16 rows whose length, strides and addresses are multiples of 8 elements: 16 bytes a thread.
+__global__ void sigmoid_mul_vec_kernel(const __nv_bfloat16* __restrict__ a, long a_stride, const __nv_bfloat16* __restrict__ g,
+                                       long g_stride, __nv_bfloat16* __restrict__ out, long out_stride, long total8, int n8) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const long t = idx / n8;
+    const int i = (int)(idx - t * n8) * 8;
+    uint4 av = *reinterpret_cast<const uint4*>(a + t * a_stride + i);
+    const uint4 gv = *reinterpret_cast<const uint4*>(g + t * g_stride + i);
+    __nv_bfloat162* ap = reinterpret_cast<__nv_bfloat162*>(&av);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 x = __bfloat1622float2(ap[k]), y = __bfloat1622float2(gp[k]);
+        ap[k] = __floats2bfloat162_rn(x.x * (1.0f / (1.0f + expf(-y.x))), x.y * (1.0f / (1.0f + expf(-y.y))));
+    }
+    *reinterpret_cast<uint4*>(out + t * out_stride + i) = av;
+}
+
 template <typename TW>
 __global__ void add_row_kernel(float* __restrict__ x, const TW* __restrict__ table_row, long total, int d) {
     pdl_launch_dependents();
@@ -583,6 +604,11 @@ ZLM_EXPORT int zlm_sigmoid_mul(const void* a, long a_stride, const void* g, long
     if (dtype == ZLM_F32)
         e = launch_pdl(sigmoid_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)a, a_stride,
                        (const float*)g, g_stride, (float*)out, out_stride, total, n);
+    else if (dtype == ZLM_BF16 && n % 8 == 0 && a_stride % 8 == 0 && g_stride % 8 == 0 && out_stride % 8 == 0 &&
+             (uintptr_t)a % 16 == 0 && (uintptr_t)g % 16 == 0 && (uintptr_t)out % 16 == 0)
+        e = launch_pdl(sigmoid_mul_vec_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream,
+                       (const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride,
+                       total / 8, n / 8);
     else if (dtype == ZLM_BF16)
         e = launch_pdl(sigmoid_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a,
                        a_stride, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, total, n);
