@@ -264,7 +264,7 @@ __global__ void norm_add_norm_kernel(const float* __restrict__ branch, const TW*
 // The norm behind a sublayer of an arrangement without norms before its sublayers, the residual sum with a
 // multiplier, and the rows the next sublayer reads (the new residual in the step's storage type):
 //   x[r] += mult * branch[r] / rms(branch[r]) * (w + off);   h[r] = x[r]      (h may be null)
-template <typename TW, typename TO>
+template <typename TW, typename TO, bool VEC>
 __global__ void norm_add_scaled_kernel(const float* __restrict__ branch, const TW* __restrict__ w, float off, float eps,
                                        float mult, float* __restrict__ x, TO* __restrict__ h, int d) {
     __shared__ float scratch[33];
@@ -273,16 +273,37 @@ __global__ void norm_add_scaled_kernel(const float* __restrict__ branch, const T
     const float* br = branch + (long)blockIdx.x * d;
     float* xr = x + (long)blockIdx.x * d;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = br[i];
-        ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = xr[i] + mult * ((br[i] * inv) * (to_float(w[i]) + off));
-        xr[i] = v;
-        if (h != nullptr) h[(long)blockIdx.x * d + i] = from_float<TO>(v);
+    if constexpr (VEC) {
+        // d is a multiple of four and every pointer keeps sixteen bytes: four elements at a time
+        const int n4 = d >> 2;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(br)[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 b4 = reinterpret_cast<const float4*>(br)[i];
+            float4 v = reinterpret_cast<const float4*>(xr)[i];
+            float ww[4];
+            load4<TW>(w + 4 * i, ww);
+            v.x += mult * ((b4.x * inv) * (ww[0] + off)); v.y += mult * ((b4.y * inv) * (ww[1] + off));
+            v.z += mult * ((b4.z * inv) * (ww[2] + off)); v.w += mult * ((b4.w * inv) * (ww[3] + off));
+            reinterpret_cast<float4*>(xr)[i] = v;
+            if (h != nullptr) store4<TO>(h + (long)blockIdx.x * d + 4 * i, v.x, v.y, v.z, v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = br[i];
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = xr[i] + mult * ((br[i] * inv) * (to_float(w[i]) + off));
+            xr[i] = v;
+            if (h != nullptr) h[(long)blockIdx.x * d + i] = from_float<TO>(v);
+        }
     }
 }
 
@@ -564,11 +585,15 @@ ZLM_EXPORT int zlm_norm_add_scaled(const float* branch, const void* w, int w_dty
                                    float* x, void* h, int h_dtype, int n_rows, int d, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (d <= 0) return ZLM_ERR_BAD_ARG;
-    const int threads = norm_threads(d);
+    const bool vec = d % 4 == 0 && (uintptr_t)branch % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                     (uintptr_t)h % 16 == 0;
+    const int threads = vec ? (d >= 2048 ? 256 : (d >= 512 ? 128 : 64)) : norm_threads(d);
     cudaError_t e;
 #define ZLM_NAS(TW, TO)                                                                                              \
-    e = launch_pdl(norm_add_scaled_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, branch, (const TW*)w, off, \
-                   eps, mult, x, (TO*)h, d)
+    e = vec ? launch_pdl(norm_add_scaled_kernel<TW, TO, true>, dim3(n_rows), dim3(threads), 0, stream, branch,         \
+                         (const TW*)w, off, eps, mult, x, (TO*)h, d)                                                 \
+            : launch_pdl(norm_add_scaled_kernel<TW, TO, false>, dim3(n_rows), dim3(threads), 0, stream, branch,        \
+                         (const TW*)w, off, eps, mult, x, (TO*)h, d)
     if (w_dtype == ZLM_F32 && (h == nullptr || h_dtype == ZLM_F32)) ZLM_NAS(float, float);
     else if (w_dtype == ZLM_F32 && h_dtype == ZLM_BF16) ZLM_NAS(float, __nv_bfloat16);
     else if (w_dtype == ZLM_BF16 && (h == nullptr || h_dtype == ZLM_F32)) ZLM_NAS(__nv_bfloat16, float);
