@@ -244,3 +244,29 @@ def test_replay_from_a_folder(tmp_path):
                 TC.rows_close(got, want[0][i:i + 1], dn, f"replay, token {i}")
         finally:
             rp.close()
+
+
+def test_replay_of_many_requests_whose_last_pages_are_nearly_empty(tmp_path):
+    """``--max-tokens`` counts tokens, the cache hands out pages of 64: six requests of 66 to 71 tokens in one batch
+    hold 411 tokens but twelve pages, and decode on together until the shorter ones have ended."""
+    from safetensors.torch import load_file
+    from test_gpu_replay import Replay
+    from ziglm_b200 import config_from_dict, write_random_model
+    cfg = TC.config("A")
+    folder = str(tmp_path / "model")
+    write_random_model(folder, config_from_dict(cfg), 9, dtype=torch.bfloat16, std=0.12, norm_jitter=0.1, device="cuda")
+    w = load_file(os.path.join(folder, "model.safetensors"))
+    reqs = [random_tokens(66 + i, cfg["vocab"], 90 + i) for i in range(6)]
+    plain = TC.plain(cfg, w, "float32")
+    want = [plain.forward(r) for r in reqs]
+    rp = Replay(folder, "float32", str(tmp_path / "logits"), max_tokens=sum(len(r) for r in reqs))
+    try:
+        first = rp.step([{"id": str(i), "tokens": r[:60], "want": [0, 59]} for i, r in enumerate(reqs)])
+        TC.rows_close(first, torch.cat([wl[[0, 59]] for wl in want]), "float32", "replay of six, first step")
+        for p in range(60, 71):
+            live = [i for i, r in enumerate(reqs) if len(r) > p]
+            got = rp.step([{"id": str(i), "tokens": [reqs[i][p]], "want": [0]} for i in live],
+                          end=[str(i) for i in live if len(reqs[i]) == p + 1])
+            TC.rows_close(got, torch.stack([want[i][p] for i in live]), "float32", f"replay of six, position {p}")
+    finally:
+        rp.close()

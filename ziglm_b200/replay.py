@@ -17,6 +17,9 @@ from .cache import PAGE_SIZE
 from .engine import Engine, EngineOptions
 
 
+MAX_LIVE_REQUESTS = 256      # slots of the replay's engine: requests alive at once
+
+
 def _parse(argv: Optional[List[str]]) -> argparse.Namespace:
     p = argparse.ArgumentParser(prog="trace_run", description=__doc__)
     p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
@@ -24,7 +27,7 @@ def _parse(argv: Optional[List[str]]) -> argparse.Namespace:
                    help="bfloat16: the kernels and precisions of serving; float32: everything in true 32-bit")
     p.add_argument("--out", required=True, help="folder the logits are written to")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help="most tokens live requests hold at any time, each request rounded up to a multiple of 64")
+                   help="most tokens live requests hold at any time (the cache adds a page of 64 per live request)")
     return p.parse_args(argv)
 
 
@@ -34,9 +37,12 @@ def main(argv: Optional[List[str]] = None, stdin=None, stdout=None) -> int:
     stdout = stdout or sys.stdout
     os.makedirs(args.out, exist_ok=True)
     max_tokens = max(PAGE_SIZE, -(-args.max_tokens // PAGE_SIZE) * PAGE_SIZE)
+    # --max-tokens counts tokens, the cache hands out pages: every live request may leave most of its last page
+    # empty, so the cache gets one page more for every request that can be alive at once
+    n_slots = max(8, min(MAX_LIVE_REQUESTS, args.max_tokens))
     # a request may be as long as the cache: a trace is a check of arithmetic, and the rotation of a position is
     # defined beyond the positions config.json says the model was trained on
-    options = EngineOptions(dtype=args.dtype, max_tokens=max_tokens, max_batch=max_tokens // PAGE_SIZE,
+    options = EngineOptions(dtype=args.dtype, max_tokens=max_tokens + n_slots * PAGE_SIZE, max_batch=n_slots,
                             max_seq_len=max_tokens, beyond_max_positions=True)
     engine = Engine.load(args.model, options)
     slot_of: Dict[str, int] = {}
