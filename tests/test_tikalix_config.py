@@ -66,6 +66,18 @@ def test_frequencies_by_hand_and_against_the_library():
     # a table of one pair whose ramp has no width: lo = hi, the pair lies on it
     f1, _ = P.rotary_frequencies({"dims": 2, "base": 7.0, "scaling": {"factor": 1.5, "original": 32, "fast": 4.0, "slow": 1.0}})
     assert f1.tolist() == [1.0]
+    # ends that cross (a short original length pushes hi below lo): the ramp is a step at lo
+    crossing = {"dims": 8, "base": 4.0, "scaling": {"factor": 2.0, "original": 7, "fast": 0.01, "slow": 1.0}}
+    fx, _ = P.rotary_frequencies(crossing)
+    pair = lambda t: 8 * math.log(7 / (2 * math.pi * t)) / (2 * math.log(4.0))
+    lo, hi = max(math.floor(pair(0.01)), 0), min(math.ceil(pair(1.0)), 7)
+    assert hi < lo
+    assert fx.tolist() == pytest.approx([4.0 ** (-2 * i / 8) * (0.5 if i > lo else 1.0) for i in range(4)])
+    cfg = TC.config("A")
+    cfg["layers"][0]["mixer"]["rot"] = crossing
+    cfg["layers"][0]["mixer"]["dim"] = 24
+    pos = config_from_dict(cfg).model_spec().layers[0].mixer.position
+    assert torch.allclose(inverse_frequencies(pos.rotary_dim, pos.theta, pos.scaling).double(), fx, rtol=1e-6, atol=0)
     for name in ("A", "B", "C"):
         conf = config_from_dict(TC.config(name))
         for layer, ls in zip(TC.config(name)["layers"], conf.model_spec().layers):

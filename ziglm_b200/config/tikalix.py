@@ -45,6 +45,7 @@ from .tumatar import _int, _num, _obj
 # Constants the design fixes.
 GATE_SLOPE = 1.702          # experts: gate * sigmoid(GATE_SLOPE * gate)
 YARN_AMPLITUDE = 0.1        # cosines and sines are multiplied by YARN_AMPLITUDE * ln(factor) + 1
+RAMP_FLOOR = 0.001          # the least width of the ramp between kept and stretched frequencies
 
 
 def _optional_num(d: Mapping[str, Any], key: str, where: str) -> Optional[float]:
@@ -156,7 +157,7 @@ class TikalixConfig:
             factor = float(sc["factor"])
             scaling = {"rope_type": "yarn", "factor": factor, "original_max_position_embeddings": float(sc["original"]),
                        "beta_fast": float(sc["fast"]), "beta_slow": float(sc["slow"]),
-                       "attention_factor": YARN_AMPLITUDE * math.log(factor) + 1.0}
+                       "attention_factor": YARN_AMPLITUDE * math.log(factor) + 1.0, "min_ramp_width": RAMP_FLOOR}
         # the amplitude belongs to the cosines and sines: a unit norm follows the rotation, and only part of a head
         # may be rotated, so it cannot be moved into the factor on the scores
         return PositionSpec(kind="rope", rotary_dim=int(rot["dims"]), theta=float(rot["base"]), scaling=scaling,

@@ -21,7 +21,8 @@ llama3: with wavelength l_i = 2*pi/f_i and L0 = original_max_position_embeddings
 yarn: the pair index at which a frequency makes r rotations over L0 positions is
     d(r) = rot * ln(L0 / (2 pi r)) / (2 ln theta);
 with lo = d(beta_fast), hi = d(beta_slow) (rounded down and up unless ``truncate`` is false, and kept inside
-[0, rot-1]; hi is raised by 0.001 if it equals lo), g_i = clamp((i - lo)/(hi - lo), 0, 1):
+[0, rot-1]; hi is raised by 0.001 if it equals lo; with ``min_ramp_width`` w the width hi - lo is max(hi - lo, w)
+instead, also where the ends cross), g_i = clamp((i - lo)/(hi - lo), 0, 1):
     f_i <- (1 - g_i) * f_i + g_i * f_i / factor
 so pairs that turn fast keep their frequency and slow ones are interpolated.  The rule also multiplies the
 rotated queries and keys by ``attention_factor`` (default 0.1 ln(factor) + 1); since the whole head is
@@ -79,7 +80,11 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[Mapping
         if scaling.get("truncate", True) is not False:
             lo, hi = math.floor(lo), math.ceil(hi)
         lo, hi = max(lo, 0), min(hi, rotary_dim - 1)
-        if lo == hi:
+        floor = scaling.get("min_ramp_width")
+        if floor is not None:
+            # the ramp's width has a floor: a ramp whose ends meet or cross (hi <= lo) is a step at lo
+            hi = lo + max(hi - lo, float(floor))
+        elif lo == hi:
             hi += 0.001
         ramp = ((torch.arange(rotary_dim // 2, dtype=torch.float64) - lo) / (hi - lo)).clamp(0.0, 1.0)
         inv = (1.0 - ramp) * inv + ramp * inv / factor
