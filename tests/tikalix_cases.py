@@ -68,7 +68,7 @@ CFG_C = {
     "layers": [
         {"type": "attention", "mixer": _att(5, 1, 12, 6, 0.6, 2.0, _rot(6, 50.0, (3.0, 16, 2.0, 0.25))),
          "mlp": _moe(20, 1.5, 3, 1, (12, 1.0))},
-        {"type": "attention", "mixer": _att(2, 2, 20, 28, 0.2, 30.0, _rot(20, 10000.0)),
+        {"type": "attention", "mixer": _att(2, 2, 20, 28, 0.2, 25.0, _rot(20, 3000.0)),
          "mlp": {"kind": "dense", "ff": 76}},
     ],
 }

@@ -72,8 +72,8 @@ def _tikalix(width: int, vocab: int, pairs: int, heads: int, kv_heads: int, dim:
              expert_ff: int) -> Dict[str, Any]:
     """A Tikalix stack of ``pairs`` times (attention + dense feed-forward, attention + experts with a shared one) with
     the heads of the Llama shape of that width: keys and values of one size, the whole head rotated and stretched
-    fourfold, a soft cap of 30."""
-    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+    fourfold, a soft cap of 50."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
              "rot": {"dims": dim, "base": 500000.0, "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
     dense = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}
     moe = {"type": "attention", "mixer": mixer,
