@@ -9,7 +9,6 @@ import os
 import pytest
 import torch
 
-import plain_tikalix as P
 import tikalix_cases as TC
 from helpers import random_tokens
 

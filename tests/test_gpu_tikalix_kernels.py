@@ -1,7 +1,6 @@
 """Each mechanism of the Tikalix design alone: the kernel (or the part) against the plain function that states its
 formula (tests/plain_tikalix.py), at sizes that are no multiple of a tile, with strided rows, several sequences in
 a step, shuffled pages, prompts and decoded tokens, and inputs made so that a fault shows."""
-import math
 from types import SimpleNamespace
 
 import pytest
@@ -43,7 +42,6 @@ def test_rotation_unit_norm_and_cache_write(dtype, H, G, hd, rot, norm_dim, scal
     T = len(positions)
     width = (H + 2 * G) * hd
     rows = _r(T, width + 24, seed=hd, dtype=dtype)
-    keep = max(norm_dim, 1)
     x = rows[:, :width].view(T, H + 2 * G, hd)
     if norm_dim and norm_dim < hd:
         x[:, :H + G, norm_dim:] = 0                     # what lies behind the true head is zero, as the weights make it

@@ -1,7 +1,6 @@
 """Tikalix without a GPU: the configuration reader and its refusals, the layout it produces, the frequency table
 against the plain implementation's and against values worked out by hand, and the plain implementation's own
 parts (router, soft cap, rotation) on cases whose answer is known."""
-import copy
 import math
 
 import pytest
