@@ -127,7 +127,7 @@ def plain(cfg: dict, w: Dict[str, torch.Tensor], dn: str):
 
 def rows_close(got: torch.Tensor, want: torch.Tensor, dn: str, what: str = "") -> None:
     """Row by row: the difference of the logits (mean taken off, root mean square over the vocabulary) relative
-    to the root mean square of the row.  float32: every row within 3e-5.  bfloat16: all rows but one in twenty-five
+    to the root mean square of the row.  float32: every row within 3e-5.  bfloat16: all rows but one in fifteen
     (or two) within 0.04 (a router's close call may send a token to another expert), and those within 1."""
     got = got.detach().float().cpu()
     want = want.detach().float().cpu()
@@ -141,5 +141,5 @@ def rows_close(got: torch.Tensor, want: torch.Tensor, dn: str, what: str = "") -
         assert err.max().item() < 3e-5, f"{what}: row {int(err.argmax())} differs by {err.max().item():.3g}"
     else:
         over = int((err > 0.04).sum())
-        assert err.max().item() < 1.0 and over <= max(2, got.shape[0] // 25), \
+        assert err.max().item() < 1.0 and over <= max(2, got.shape[0] // 15), \
             f"{what}: {over} of {got.shape[0]} rows differ, the worst (row {int(err.argmax())}) by {err.max().item():.3g}"

@@ -203,6 +203,10 @@ struct AtcCommon {
     const int* block_table;
     int bt_stride;
     int* err;
+    // the flat decode kernel only: out[t, h, d] is multiplied by sigmoid(gate[t * gate_stride + h * hd + d]) before it
+    // is rounded (a gate on the heads' outputs); null: none
+    const __nv_bfloat16* gate;
+    long gate_stride;
 };
 
 // The producer warp: copies the pages [page_lo, page_hi) of one kv head into the ring.
@@ -371,6 +375,11 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
         }
         out[row * HD + d] = __float2bfloat16_rn(acc / den);
     }
+}
+
+// sigmoid of a gate element, or 1 without a gate
+__device__ __forceinline__ float gate_factor(const __nv_bfloat16* g, long i) {
+    return g == nullptr ? 1.0f : 1.0f / (1.0f + __expf(-__bfloat162float(g[i])));
 }
 
 // ------------------------------------------------------------- decode, flat
@@ -711,6 +720,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         const int first_block = (int)(s_i / chunk);
         const int pieces = (int)((s_i + p_t - 1) / chunk) - first_block + 1;
         __nv_bfloat16* orow = out + ((long)t * a.n_heads + (long)kvh * group) * HD;
+        const __nv_bfloat16* grow = a.gate ? a.gate + (long)t * a.gate_stride + (long)kvh * group * HD : nullptr;
         if (!dead) {
             float* slot = slots + (long)(blockIdx.x + item) * slot_floats;
             for (int idx = threadIdx.x; idx < group * HD; idx += ATC_CONSUMERS * 32) {
@@ -727,7 +737,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
                     den += ml[w * 16 + r] * wgt;
                 }
                 if (pieces == 1) {
-                    orow[r * HD + d] = __float2bfloat16_rn(acc / den);
+                    orow[r * HD + d] = __float2bfloat16_rn(acc / den * gate_factor(grow, idx));
                 } else {
                     slot[idx] = acc;
                     if (d == 0) { slot[group * HD + 2 * r] = big; slot[group * HD + 2 * r + 1] = den; }
@@ -776,8 +786,10 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
                             acc.x += v[u].x * w; acc.y += v[u].y * w; acc.z += v[u].z * w; acc.w += v[u].w * w;
                         }
                         const float inv = 1.f / den;
-                        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-                        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                        acc.x *= inv * gate_factor(grow, 4 * f); acc.y *= inv * gate_factor(grow, 4 * f + 1);
+                        acc.z *= inv * gate_factor(grow, 4 * f + 2); acc.w *= inv * gate_factor(grow, 4 * f + 3);
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
                         uint2 packed;
                         packed.x = *reinterpret_cast<uint32_t*>(&lo);
                         packed.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -828,6 +840,8 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
                                 acc.x += v[u].x * w; acc.y += v[u].y * w; acc.z += v[u].z * w; acc.w += v[u].w * w;
                             }
                         }
+                        acc.x *= gate_factor(grow, 4 * f); acc.y *= gate_factor(grow, 4 * f + 1);
+                        acc.z *= gate_factor(grow, 4 * f + 2); acc.w *= gate_factor(grow, 4 * f + 3);
                         __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
                         uint2 packed;
                         packed.x = *reinterpret_cast<uint32_t*>(&lo);
@@ -848,7 +862,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
                             acc += __ldcg(first + sidx * step + idx) * wgt;
                             den += __ldcg(ml_r + sidx * step + 1) * wgt;
                         }
-                        orow[r * HD + d] = __float2bfloat16_rn(acc / den);
+                        orow[r * HD + d] = __float2bfloat16_rn(acc / den * gate_factor(grow, idx));
                     }
                 }
             }
@@ -1058,6 +1072,8 @@ static int fill_common(AtcCommon* a, CUtensorMap* mk, CUtensorMap* mv, const voi
     a->block_table = block_table;
     a->bt_stride = bt_stride;
     a->err = att_error_word();
+    a->gate = nullptr;
+    a->gate_stride = 0;
     return 0;
 }
 
@@ -1161,7 +1177,7 @@ ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void*
                                          const void* k_pages, const void* v_pages, long n_pages, int page_size,
                                          int n_blocks, int* counters, float* scratch, long scratch_floats,
                                          int rope_fused, int rope_store, int rot, const float* inv_freq,
-                                         cudaStream_t stream) {
+                                         const void* gate, long gate_stride, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (T > FLAT_MAX_TOKENS) return ZLM_ERR_UNSUPPORTED;
     if (n_kv > 0 && n_heads / n_kv > 16) return ZLM_ERR_UNSUPPORTED;
@@ -1178,6 +1194,8 @@ ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void*
     int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
                          k_pages, v_pages, n_pages, page_size, softcap);
     if (rc) return rc;
+    a.gate = (const __nv_bfloat16*)gate;          // bf16 [T, gate_stride]: the heads' outputs times its sigmoid
+    a.gate_stride = gate_stride;
     const int group = n_heads / n_kv;
     int smem = 0;
     const int resident = hd == 128 ? flat_blocks<128>(group, T, &smem) : flat_blocks<64>(group, T, &smem);
@@ -1336,6 +1354,8 @@ ZLM_EXPORT int zlm_attention_decode_noalloc(const void* q, long q_row_stride, vo
     a.block_table = block_table;
     a.bt_stride = bt_stride;
     a.err = err;
+    a.gate = nullptr;
+    a.gate_stride = 0;
     dim3 grid(n_splits, n_kv, T);
     if (hd == 128) {
         attn_decode_kernel<128><<<grid, ATC_THREADS, DecodeCfg<128>::SMEM, stream>>>(mk, mv, a, positions,

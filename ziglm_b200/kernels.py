@@ -108,7 +108,7 @@ _PROTOTYPES = {
                                  c_void_p, c_void_p],
         "zlm_attention_decode_flat": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
-                                      c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p],
+                                      c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p],
         "zlm_attention_decode_flat_blocks": [c_int, c_int, c_int, c_int],
         "zlm_attention_decode_flat_scratch": [c_int, c_int, c_int, c_int, c_int],
         "zlm_attention_prefill": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
@@ -119,7 +119,7 @@ _PROTOTYPES = {
     "attention_fmha": {
         "zlm_attention_prefill_fmha": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                        c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int,
-                                       c_void_p],
+                                       c_void_p, c_long, c_void_p],
         "zlm_attention_fmha_status": [c_void_p],
         "zlm_attention_fmha_wait_selftest": [c_int, c_void_p, c_void_p],
     },
@@ -760,6 +760,16 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: i
     return True
 
 
+def _gate_args(gate: Optional[torch.Tensor], n_rows: int, width: int):
+    """(pointer, row stride) of a bf16 gate [n_rows, width] that may be a column slice; (None, 0) without one."""
+    if gate is None:
+        return None, 0
+    _rows(gate, "gate")
+    if gate.dtype != torch.bfloat16 or gate.shape[0] < n_rows or gate.shape[1] != width:
+        raise KernelError("attention: the gate must be bfloat16 with a row per token and a column per output element")
+    return gate.data_ptr(), _row_stride(gate)
+
+
 def attention_decode_flat_blocks(n_tokens: int, n_heads: int, n_kv: int, head_dim: int) -> int:
     """Blocks of one resident wave of the flat decode kernel for a step of ``n_tokens`` (0: sizes it refuses)."""
     return int(_fn("attention_tc", "zlm_attention_decode_flat_blocks")(n_tokens, n_heads, n_kv, head_dim))
@@ -774,7 +784,8 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
                           window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                           block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
                           n_blocks: int, counters: torch.Tensor, scratch: torch.Tensor,
-                          rope: Optional[Tuple[Optional[torch.Tensor], int, bool]] = None, softcap: float = 0.0) -> bool:
+                          rope: Optional[Tuple[Optional[torch.Tensor], int, bool]] = None, softcap: float = 0.0,
+                          gate: Optional[torch.Tensor] = None) -> bool:
     """Tensor-core attention for steps of one token per sequence, with the pages of all sequences of the
     step divided evenly over ``n_blocks`` blocks (one resident wave), whatever the sequences' lengths.  One
     launch: the block that finishes a sequence's last piece merges the pieces.
@@ -788,6 +799,9 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
     then [q heads | k heads | v heads] (k and v only with ``store``) as the projection left them; the query
     heads are rotated as they are loaded (``qkv`` itself is left alone) and, with ``store``, the new keys
     (rotated) and values go into the cache pages.  rotary_dim must be a multiple of 32.
+
+    ``gate`` (bf16 [T, n_heads * head_dim], may be a column slice): the output is multiplied by its sigmoid before
+    it is rounded.
     """
     _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
     _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
@@ -821,7 +835,8 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
         int(window or 0),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
         k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_blocks, counters.data_ptr(),
-        scratch.data_ptr(), scratch.numel(), fused, int(bool(store)), int(rot), _ptr(inv_freq), _stream())
+        scratch.data_ptr(), scratch.numel(), fused, int(bool(store)), int(rot), _ptr(inv_freq),
+        *_gate_args(gate, T, n_heads * head_dim), _stream())
     if status == -2:
         return False
     if status == -1:
@@ -860,9 +875,10 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new
 def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
                            head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
                            past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                           v_pages: torch.Tensor, page_size: int, softcap: float = 0.0) -> bool:
+                           v_pages: torch.Tensor, page_size: int, softcap: float = 0.0,
+                           gate: Optional[torch.Tensor] = None) -> bool:
     """Prompt attention on the tcgen05 tensor cores (tiles of 128 queries, accumulators in tensor memory); same
-    arguments as :func:`attention_prefill`.  False if refused."""
+    arguments as :func:`attention_prefill`, and ``gate`` as in :func:`attention_decode_flat`.  False if refused."""
     _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
     _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(past_lens, "past_lens", torch.int32)
     _cuda(block_table, "block_table", torch.int32)
@@ -877,7 +893,8 @@ def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, ma
     status = _fn("attention_fmha", "zlm_attention_prefill_fmha")(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
         float(softcap or 0.0), int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
-        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, _stream())
+        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size,
+        *_gate_args(gate, out.shape[0], n_heads * head_dim), _stream())
     if status == -2:
         return False
     _check(status, "attention_prefill_fmha")
@@ -932,9 +949,11 @@ def attention_with_rope(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int
 
 
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
-              window: Optional[int], io, softcap: float = 0.0) -> None:
+              window: Optional[int], io, softcap: float = 0.0, gate: Optional[torch.Tensor] = None) -> bool:
     """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``softcap`` c > 0:
-    the scaled scores become c * tanh(score / c)."""
+    the scaled scores become c * tanh(score / c).  ``gate`` ([T, n_heads * head_dim] of the step's type): the kernels
+    that can multiply their output by sigmoid(gate) before rounding it; the result says whether that was done (the
+    caller multiplies when it was not)."""
     if _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
         if n_blocks > 0:
@@ -943,8 +962,8 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
             counters = step.ws.buf("attn_flat_counters", (step.n_tokens * n_kv,), torch.int32, zeros=True)
             if attention_decode_flat(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions,
                                      step.seq_of_token, io.block_table, io.k_pages, io.v_pages, io.page_size,
-                                     n_blocks, counters, scratch, softcap=softcap):
-                return
+                                     n_blocks, counters, scratch, softcap=softcap, gate=gate):
+                return gate is not None
         if step.single_token:
             n_splits = decode_splits(step.n_tokens, n_kv, step.max_total, io.page_size)
             part_o = step.ws.buf("attn_part_o", (step.n_tokens * n_heads * n_splits * head_dim,), torch.float32)
@@ -952,20 +971,21 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
             if attention_decode(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions,
                                 step.seq_of_token, io.block_table, io.k_pages, io.v_pages, io.page_size, n_splits,
                                 part_o, part_ml, softcap=softcap):
-                return
+                return False
         else:
             # prompts: the tcgen05 kernel (tiles of 128 queries); a handful of tokens: the 64-row mma.sync one
             args = (qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window, step.cu_seqlens,
                     step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size)
-            if step.max_new >= 16 and attention_prefill_fmha(*args, softcap=softcap):
-                return
+            if step.max_new >= 16 and attention_prefill_fmha(*args, softcap=softcap, gate=gate):
+                return gate is not None
             if attention_prefill(*args, softcap=softcap):
-                return
+                return False
     max_keys = min(step.max_total, window) if window else step.max_total
     need = attention_general_scratch(step.n_tokens, n_heads, n_kv, head_dim, max_keys)
     scratch = step.ws.buf("attn_parts", (need,), torch.float32) if need > 0 else None
     attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
                       io.block_table, io.k_pages, io.v_pages, io.page_size, max_keys, scratch, softcap=softcap)
+    return False
 
 
 def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1, softcap: float = 0.0):

@@ -136,9 +136,10 @@ class CappedAttention(Part):
                                 io.k_pages if io.writes_cache else None, io.v_pages if io.writes_cache else None,
                                 io.page_size)
         out = step.ws.buf("attn_out", (T, H * P), self.dtype)
-        kernels.attention(step, proj, out, H, G, P, self.scale, None, io, softcap=self.softcap)
-        if self.gated:
-            kernels.sigmoid_mul(out, proj[:, (H + 2 * G) * P:], out)
+        gate = proj[:, (H + 2 * G) * P:] if self.gated else None
+        # the tensor-core kernels of prompts and of decode steps multiply by the gate's sigmoid as they store
+        if not kernels.attention(step, proj, out, H, G, P, self.scale, None, io, softcap=self.softcap, gate=gate) and self.gated:
+            kernels.sigmoid_mul(out, gate, out)
         self.o(out, residual, accumulate=accumulate)
         return None
 
