@@ -117,12 +117,12 @@ def test_attention_with_a_soft_cap(dtype, H, G, hd, cap):
         kernels.attention(step, q, out, H, G, hd, scale, None, io, softcap=cap or 0.0)
         ref = torch.cat([w[p:p + n] for w, p, n in zip(want, past, new)])
         torch.testing.assert_close(out.float().cpu(), ref, **_tol(dtype, (2e-5, 1e-4), (2e-2, 2e-2)))
-        # a gate on the heads' outputs (a column slice of wider rows): the tensor-core kernels of prompts and of
-        # decode steps multiply by its sigmoid as they store and say so; the others leave the output as it is
+        # a gate on the heads' outputs (a column slice of wider rows): the flat decode kernel multiplies by its
+        # sigmoid as it stores and says so; the others leave the output as it is
         gate = _r(T, H * hd + 16, seed=11, scale=2.0, dtype=dtype)[:, 16:]
         out.fill_(7.0)
         applied = kernels.attention(step, q, out, H, G, hd, scale, None, io, softcap=cap or 0.0, gate=gate)
-        assert applied == (dtype == torch.bfloat16 and hd in (64, 128))
+        assert applied == (dtype == torch.bfloat16 and hd in (64, 128) and new == [1, 1])
         gated = ref * torch.sigmoid(gate.float().cpu()) if applied else ref
         torch.testing.assert_close(out.float().cpu(), gated, **_tol(dtype, (2e-5, 1e-4), (2e-2, 2e-2)))
     if cap:

@@ -73,9 +73,6 @@ struct FmArgs {
     const int* cu_seqlens;
     const int* past_lens;
     int* err;
-    // out[t, h, d] is multiplied by sigmoid(gate[t * gate_stride + h * hd + d]) before it is rounded; null: none
-    const __nv_bfloat16* gate;
-    long gate_stride;
 };
 
 // The softmax of one query row over a step of NP pages: S from tensor memory, P (bf16) back over its first
@@ -410,8 +407,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             tc_fence_after_sync();
             const float inv = 1.0f / l;
             __nv_bfloat16* orow = a.out + ((long)(tok_begin + q0 + t * FM_BQ + r) * a.n_heads + h) * HD;
-            const __nv_bfloat16* grow =
-                a.gate ? a.gate + (long)(tok_begin + q0 + t * FM_BQ + r) * a.gate_stride + (long)h * HD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t v[32];
@@ -420,17 +415,6 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (real) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        if (grow != nullptr) {
-                            // the gate's eight elements for these eight outputs (the rows keep 16 bytes)
-                            const uint4 gv = *reinterpret_cast<const uint4*>(grow + c * 32 + g * 8);
-                            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const float2 gf = __bfloat1622float2(gp[k]);
-                                v[g * 8 + 2 * k] = __float_as_uint(__uint_as_float(v[g * 8 + 2 * k]) / (1.0f + __expf(-gf.x)));
-                                v[g * 8 + 2 * k + 1] = __float_as_uint(__uint_as_float(v[g * 8 + 2 * k + 1]) / (1.0f + __expf(-gf.y)));
-                            }
-                        }
                         uint4 pk;
                         __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
                         __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
@@ -543,15 +527,13 @@ using namespace zlm;
 
 // Prompt attention: B sequences with cu_seqlens[B+1] new tokens each after past_lens[b] cached ones.
 // q: bf16 [T, q_row_stride], the query heads first in each row; out: bf16 [T, n_heads * hd].
-// softcap c > 0: the scaled scores become c tanh(score / c); 0: none.  gate (bf16 [T, gate_stride], may be null): the
-// output of head h of token t is multiplied by sigmoid(gate[t, h * hd ..]) before it is rounded.
+// softcap c > 0: the scaled scores become c tanh(score / c); 0: none.
 ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long total_tokens, void* out, int B,
                                           int max_new, int n_heads, int n_kv, int hd, float scale, float softcap,
                                           int window, const int* cu_seqlens, const int* past_lens, const int* block_table,
                                           int bt_stride, const void* k_pages, const void* v_pages, long n_pages,
-                                          int page_size, const void* gate, long gate_stride, cudaStream_t stream) {
+                                          int page_size, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
-    if (gate != nullptr && (((uintptr_t)gate % 16) || (gate_stride % 8))) return ZLM_ERR_UNSUPPORTED;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size != FM_PAGE || total_tokens <= 0) return ZLM_ERR_BAD_ARG;
     if (hd != 64 && hd != 128) return ZLM_ERR_UNSUPPORTED;
     if (!(scale > 0.f)) return ZLM_ERR_UNSUPPORTED;            // the row maximum is taken before scaling
@@ -580,8 +562,6 @@ ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long
     a.cu_seqlens = cu_seqlens;
     a.past_lens = past_lens;
     a.err = fm_error_word();
-    a.gate = (const __nv_bfloat16*)gate;
-    a.gate_stride = gate_stride;
     return hd == 128 ? fm_launch<128>(mq, mk, mv, a, grid, stream) : fm_launch<64>(mq, mk, mv, a, grid, stream);
 }
 

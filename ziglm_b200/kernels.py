@@ -119,7 +119,7 @@ _PROTOTYPES = {
     "attention_fmha": {
         "zlm_attention_prefill_fmha": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                        c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int,
-                                       c_void_p, c_long, c_void_p],
+                                       c_void_p],
         "zlm_attention_fmha_status": [c_void_p],
         "zlm_attention_fmha_wait_selftest": [c_int, c_void_p, c_void_p],
     },
@@ -875,10 +875,9 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new
 def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
                            head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
                            past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                           v_pages: torch.Tensor, page_size: int, softcap: float = 0.0,
-                           gate: Optional[torch.Tensor] = None) -> bool:
+                           v_pages: torch.Tensor, page_size: int, softcap: float = 0.0) -> bool:
     """Prompt attention on the tcgen05 tensor cores (tiles of 128 queries, accumulators in tensor memory); same
-    arguments as :func:`attention_prefill`, and ``gate`` as in :func:`attention_decode_flat`.  False if refused."""
+    arguments as :func:`attention_prefill`.  False if refused."""
     _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
     _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(past_lens, "past_lens", torch.int32)
     _cuda(block_table, "block_table", torch.int32)
@@ -893,8 +892,7 @@ def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, ma
     status = _fn("attention_fmha", "zlm_attention_prefill_fmha")(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
         float(softcap or 0.0), int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
-        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size,
-        *_gate_args(gate, out.shape[0], n_heads * head_dim), _stream())
+        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, _stream())
     if status == -2:
         return False
     _check(status, "attention_prefill_fmha")
@@ -951,9 +949,10 @@ def attention_with_rope(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
               window: Optional[int], io, softcap: float = 0.0, gate: Optional[torch.Tensor] = None) -> bool:
     """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``softcap`` c > 0:
-    the scaled scores become c * tanh(score / c).  ``gate`` ([T, n_heads * head_dim] of the step's type): the kernels
-    that can multiply their output by sigmoid(gate) before rounding it; the result says whether that was done (the
-    caller multiplies when it was not)."""
+    the scaled scores become c * tanh(score / c).  ``gate`` ([T, n_heads * head_dim] of the step's type): the flat
+    decode kernel multiplies its output by sigmoid(gate) before rounding it; the result says whether that was done
+    (the caller multiplies when it was not: in a prompt one pass of ``sigmoid_mul`` over coalesced rows costs less
+    than the same work in the prompt kernel's epilogue, where every thread walks a row of its own)."""
     if _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
         if n_blocks > 0:
@@ -976,8 +975,8 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
             # prompts: the tcgen05 kernel (tiles of 128 queries); a handful of tokens: the 64-row mma.sync one
             args = (qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window, step.cu_seqlens,
                     step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size)
-            if step.max_new >= 16 and attention_prefill_fmha(*args, softcap=softcap, gate=gate):
-                return gate is not None
+            if step.max_new >= 16 and attention_prefill_fmha(*args, softcap=softcap):
+                return False
             if attention_prefill(*args, softcap=softcap):
                 return False
     max_keys = min(step.max_total, window) if window else step.max_total

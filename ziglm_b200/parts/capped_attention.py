@@ -137,7 +137,7 @@ class CappedAttention(Part):
                                 io.page_size)
         out = step.ws.buf("attn_out", (T, H * P), self.dtype)
         gate = proj[:, (H + 2 * G) * P:] if self.gated else None
-        # the tensor-core kernels of prompts and of decode steps multiply by the gate's sigmoid as they store
+        # the flat decode kernel multiplies by the gate's sigmoid as it stores; behind the others a kernel does
         if not kernels.attention(step, proj, out, H, G, P, self.scale, None, io, softcap=self.softcap, gate=gate) and self.gated:
             kernels.sigmoid_mul(out, gate, out)
         self.o(out, residual, accumulate=accumulate)
